@@ -1,0 +1,227 @@
+"""CPU oracle for GDPA (Generalized Dot Product Attention). TEST INFRASTRUCTURE ONLY.
+
+This file restates, in eager PyTorch fp32 on the CPU, the algorithm the reference library
+defines for jagged GDPA.  It exists so that the CUDA kernels can be checked against it; it is
+never imported by the shipped package (only by tests, the smoke check and the CPU-baseline leg
+of the benchmark).
+
+Parity pin: the reference stores no golden tensors for this path.  The restatement is pinned
+against outputs of the reference's own Python code run on the CPU (committed under
+``tests/golden/`` together with the script that produced them):
+
+* ``cpu_generalized_dot_product_attention`` (softmax, no scale, separate Q / KV offsets),
+  gdpa/triton/triton_generalized_dot_product_attention.py:3898-3979;
+* the eager helper ``_gdpa_reference`` (act(q kT) v per sequence, fp32),
+  gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:35-47, with the activation table
+  ``get_pytorch_activation``, gdpa/triton/math.py:58-74.
+
+What those two do not pin (the reference has no CPU code for it) is the placement of
+``qk_scale``; it follows the reference's device kernels: ``p = act(qk); p *= qk_scale``
+(gdpa/triton/triton_generalized_dot_product_attention.py:279-307) and, in the backward,
+``dS = qk_scale * act'(S) * dP`` (:1626-1634).  Gradients come from autograd over the forward
+below, which is the same chain rule.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+# Activation names and integer ids of the reference, in enumeration order
+# (gdpa/triton/math.py:43-55 and :77-78).  "softmax" is not in the reference enum; it is the
+# name this library gives to the behaviour of the reference's CPU kernel.
+ACTIVATION_IDS: Dict[str, int] = {
+    "raw": 0,
+    "gelu": 1,
+    "gelu_approx": 2,
+    "fast_gelu": 3,
+    "leaky_relu": 4,
+    "relu": 5,
+    "fast_gelu_bf16": 6,
+    "silu": 7,
+    "fast_silu": 8,
+    "hardswish": 9,
+    "relu_square": 10,
+    "fast_gelu_taylor_approx": 11,
+}
+
+
+def pytorch_activation(name: str) -> Callable[[torch.Tensor], torch.Tensor]:
+    """Eager activation for a reference activation name (gdpa/triton/math.py:58-74)."""
+    if name not in ACTIVATION_IDS:
+        # same error class and wording as activation_string_to_int, gdpa/triton/math.py:81-85
+        raise ValueError(f"Unsupported activation function: {name}")
+    if name == "raw":
+        return lambda x: x
+    if name == "gelu":
+        return lambda x: F.gelu(x)
+    if name in ("gelu_approx", "fast_gelu", "fast_gelu_bf16", "fast_gelu_taylor_approx"):
+        return lambda x: F.gelu(x, approximate="tanh")
+    if name == "leaky_relu":
+        return lambda x: F.leaky_relu(x, 0.01)
+    if name == "relu":
+        return torch.relu
+    if name in ("silu", "fast_silu"):
+        return F.silu
+    if name == "hardswish":
+        return F.hardswish
+    if name == "relu_square":
+        return lambda x: torch.relu(x) * torch.relu(x)
+    raise AssertionError(name)
+
+
+def gdpa_forward(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    activation: str = "raw",
+    qk_scale: Optional[float] = None,
+    p_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """O[b] = (act(Q_b K_b^T) * qk_scale) V_b per sequence and head, in fp32.
+
+    Loop, slicing and transposes follow cpu_generalized_dot_product_attention
+    (gdpa/triton/triton_generalized_dot_product_attention.py:3950-3979); the activation and the
+    post-activation scale follow the device kernel (:279-307).  ``activation="softmax"``
+    computes softmax(qk_scale * S) V, which for ``qk_scale=None`` is exactly the reference CPU
+    kernel (:3973-3975).
+
+    ``p_dtype`` optionally rounds P to that dtype before the second contraction, as the device
+    kernels do (:307); the default keeps fp32 throughout.
+    """
+    scale = 1.0 if qk_scale is None else float(qk_scale)  # :3148-3149
+    q = query.to(torch.float32)
+    k = key.to(torch.float32)
+    v = value.to(torch.float32)
+    out = torch.zeros_like(q)
+    bs = query_offset.numel() - 1
+    act = None if activation == "softmax" else pytorch_activation(activation)
+    for i in range(bs):
+        qs, qe = int(query_offset[i]), int(query_offset[i + 1])
+        ks, ke = int(key_offset[i]), int(key_offset[i + 1])
+        if qe <= qs:
+            continue
+        q_i = q[qs:qe].transpose(0, 1)  # [H, Lq, D]
+        k_i = k[ks:ke].transpose(0, 1)
+        v_i = v[ks:ke].transpose(0, 1)
+        s = torch.matmul(q_i, k_i.transpose(-2, -1))
+        if act is None:
+            if ke > ks:
+                p = F.softmax(s * scale, dim=-1)
+            else:
+                p = s
+        else:
+            p = act(s) * scale
+        if p_dtype is not None:
+            p = p.to(p_dtype).to(torch.float32)
+        o_i = torch.matmul(p, v_i)
+        out[qs:qe] = o_i.transpose(0, 1)
+    return out
+
+
+def gdpa_forward_backward(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    grad_out: torch.Tensor,
+    activation: str = "raw",
+    qk_scale: Optional[float] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(O, dQ, dK, dV) in fp32 by autograd over :func:`gdpa_forward`.
+
+    Equivalent to the hand formulas of the reference backward: dP = dO V^T,
+    dS = qk_scale act'(S) dP, dV = (qk_scale act(S))^T dO, dK = dS^T Q, dQ = dS K
+    (gdpa/triton/triton_generalized_dot_product_attention.py:1602-1634, :1761-1805).
+    """
+    q = query.detach().to(torch.float32).clone().requires_grad_(True)
+    k = key.detach().to(torch.float32).clone().requires_grad_(True)
+    v = value.detach().to(torch.float32).clone().requires_grad_(True)
+    o = gdpa_forward(q, k, v, query_offset, key_offset, activation, qk_scale)
+    o.backward(grad_out.to(torch.float32))
+    zero = torch.zeros_like
+    return (
+        o.detach(),
+        q.grad if q.grad is not None else zero(q),
+        k.grad if k.grad is not None else zero(k),
+        v.grad if v.grad is not None else zero(v),
+    )
+
+
+def gdpa_backward_formulas(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    grad_out: torch.Tensor,
+    activation: str,
+    qk_scale: Optional[float] = None,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dQ, dK, dV) from the closed-form derivative tables of the reference
+    (gdpa/triton/math.py:196-206 tanh-GELU, :359-367 SiLU, relu / raw / relu_square / leaky_relu
+    / hardswish / erf-GELU likewise), used to cross-check the autograd route on the CPU."""
+    scale = 1.0 if qk_scale is None else float(qk_scale)
+    q = query.to(torch.float32)
+    k = key.to(torch.float32)
+    v = value.to(torch.float32)
+    do = grad_out.to(torch.float32)
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    for i in range(query_offset.numel() - 1):
+        qs, qe = int(query_offset[i]), int(query_offset[i + 1])
+        ks, ke = int(key_offset[i]), int(key_offset[i + 1])
+        if qe <= qs or ke <= ks:
+            continue
+        q_i = q[qs:qe].transpose(0, 1)
+        k_i = k[ks:ke].transpose(0, 1)
+        v_i = v[ks:ke].transpose(0, 1)
+        do_i = do[qs:qe].transpose(0, 1)
+        s = q_i @ k_i.transpose(-2, -1)
+        p, dact = activation_and_grad(s, activation)
+        dp = do_i @ v_i.transpose(-2, -1)
+        ds = dact * dp * scale
+        dv[ks:ke] = ((p * scale).transpose(-2, -1) @ do_i).transpose(0, 1)
+        dk[ks:ke] = (ds.transpose(-2, -1) @ q_i).transpose(0, 1)
+        dq[qs:qe] = (ds @ k_i).transpose(0, 1)
+    return dq, dk, dv
+
+
+def activation_and_grad(x: torch.Tensor, name: str) -> Tuple[torch.Tensor, torch.Tensor]:
+    """act(x) and act'(x) from the reference's closed forms (gdpa/triton/math.py:99-413)."""
+    if name == "raw":
+        return x, torch.ones_like(x)
+    if name == "relu":
+        return torch.relu(x), (x > 0).to(x.dtype)
+    if name == "leaky_relu":
+        return F.leaky_relu(x, 0.01), torch.where(x > 0, 1.0, 0.01).to(x.dtype)
+    if name == "relu_square":
+        r = torch.relu(x)
+        return r * r, 2.0 * r
+    if name in ("gelu_approx", "fast_gelu", "fast_gelu_bf16", "fast_gelu_taylor_approx"):
+        c0, c1 = 0.7978845608028654, 0.044715
+        t = torch.tanh(c0 * x * (1.0 + c1 * x * x))
+        return 0.5 * x * (1.0 + t), 0.5 * x * (1.0 - t * t) * (c0 + 3.0 * c0 * c1 * x * x) + 0.5 * (1.0 + t)
+    if name == "gelu":
+        cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
+        pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
+        return x * cdf, cdf + x * pdf
+    if name in ("silu", "fast_silu"):
+        sg = torch.sigmoid(x)
+        return x * sg, sg * (1.0 + x * (1.0 - sg))
+    if name == "hardswish":
+        y = F.hardswish(x)
+        g = torch.where(x < -3.0, 0.0, torch.where(x > 3.0, 1.0, (2.0 * x + 3.0) / 6.0))
+        return y, g.to(x.dtype)
+    raise ValueError(f"Unsupported activation function: {name}")
+
+
+def useful_flops(q_lens: Sequence[int], kv_lens: Sequence[int], heads: int, head_dim: int, mode: str = "fwd") -> int:
+    """Useful FLOPs over valid jagged pairs only: 4 H D sum(Lq Lkv) forward, x2.5 backward,
+    x3.5 forward+backward (gdpa/scripts/benchmark.py:212-222, :668-674)."""
+    pairs = sum(int(a) * int(b) for a, b in zip(q_lens, kv_lens))
+    fwd = 4 * heads * head_dim * pairs
+    return {"fwd": fwd, "bwd": fwd * 5 // 2, "fwd_bwd": fwd * 7 // 2}[mode]

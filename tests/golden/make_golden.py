@@ -1,0 +1,93 @@
+"""Generate the golden fixtures of this folder by running the reference library's own Python
+code on the CPU.  Needs a checkout of the reference; run as
+
+    python tests/golden/make_golden.py /path/to/ads_model_kernel_library
+
+The reference uses absolute imports ``ads_mkl.ops.oss.<package>``; a temporary directory with a
+symlink of that name makes them resolve.  Three things are recorded:
+
+* ``reference_cpu_softmax``: outputs of ``cpu_generalized_dot_product_attention``
+  (gdpa/triton/triton_generalized_dot_product_attention.py:3898-3979) on a jagged batch with
+  different Q and KV lengths;
+* ``reference_eager_<activation>``: outputs of the eager helper ``_gdpa_reference``
+  (gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:35-47), executed from the reference's file
+  with the reference's activation table ``get_pytorch_activation`` (gdpa/triton/math.py:58-74);
+  the helper's module cannot be imported whole because it needs a Triton fork, so the single
+  function is taken from its source by ``ast`` and executed unchanged;
+* ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
+
+Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
+"""
+from __future__ import annotations
+
+import ast
+import json
+import os
+import sys
+import tempfile
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main(ref_root: str) -> None:
+    shim = tempfile.mkdtemp(prefix="ads_mkl_shim_")
+    os.makedirs(os.path.join(shim, "ads_mkl", "ops"))
+    os.symlink(os.path.abspath(ref_root), os.path.join(shim, "ads_mkl", "ops", "oss"))
+    sys.path.insert(0, shim)
+
+    from ads_mkl.ops.oss.gdpa.triton import math as ref_math  # noqa: E402
+    import ads_mkl.ops.oss.gdpa.triton.triton_generalized_dot_product_attention as ref_gdpa  # noqa: E402
+
+    out = {}
+
+    # ---- 1. the registered CPU kernel (softmax), Q and KV lengths differ -------------------
+    rng = np.random.default_rng(1234)
+    B, H, D = 5, 2, 16
+    lq = rng.integers(1, 20, B)
+    lk = rng.integers(1, 24, B)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]), dtype=torch.int64)
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]), dtype=torch.int64)
+    g = torch.Generator().manual_seed(1234)
+    q = torch.randn(int(qo[-1]), H, D, generator=g)
+    k = torch.randn(int(ko[-1]), H, D, generator=g)
+    v = torch.randn(int(ko[-1]), H, D, generator=g)
+    o = ref_gdpa.cpu_generalized_dot_product_attention(
+        q, k, v, qo, ko, int(lq.max()), int(lk.max()), activation="raw"
+    )
+    out.update(
+        softmax_q=q.numpy(), softmax_k=k.numpy(), softmax_v=v.numpy(),
+        softmax_qo=qo.numpy(), softmax_ko=ko.numpy(), softmax_out=o.numpy(),
+    )
+
+    # ---- 2. the eager helper, every activation of the table --------------------------------
+    src_path = os.path.join(ref_root, "gdpa_megakernel", "tests", "test_tlx_gdpa_megakernel.py")
+    tree = ast.parse(open(src_path).read())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "_gdpa_reference")
+    ns = {"torch": torch, "get_pytorch_activation": ref_math.get_pytorch_activation}
+    exec(compile(ast.Module(body=[fn], type_ignores=[]), src_path, "exec"), ns)
+    helper = ns["_gdpa_reference"]
+
+    rng = np.random.default_rng(4321)
+    B, H, D = 4, 2, 16
+    ln = rng.integers(1, 24, B)
+    off = torch.tensor(np.concatenate([[0], np.cumsum(ln)]), dtype=torch.int64)
+    g = torch.Generator().manual_seed(4321)
+    q = torch.randn(int(off[-1]), H, D, generator=g)
+    k = torch.randn(int(off[-1]), H, D, generator=g)
+    v = torch.randn(int(off[-1]), H, D, generator=g)
+    out.update(eager_q=q.numpy(), eager_k=k.numpy(), eager_v=v.numpy(), eager_off=off.numpy())
+    for act in ref_math.Activation:
+        out[f"eager_out_{act.value}"] = helper(q, k, v, off, act).numpy()
+
+    np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
+    ids = {a.value: i for a, i in ref_math.activation_to_int.items()}
+    with open(os.path.join(HERE, "activation_ids.json"), "w") as f:
+        json.dump(ids, f, indent=1)
+    print("wrote", len(out), "arrays;", ids)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

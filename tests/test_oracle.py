@@ -1,0 +1,73 @@
+"""The CPU oracle against the golden vectors produced by the reference's own Python code
+(tests/golden/make_golden.py), and internal consistency of the oracle (autograd route against the
+closed-form derivative tables)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gdpa_oracle as orc
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_activation_ids_match_reference_table():
+    ids = json.load(open(os.path.join(HERE, "golden", "activation_ids.json")))
+    assert ids == orc.ACTIVATION_IDS
+
+
+def test_softmax_matches_reference_cpu_kernel(golden):
+    t = lambda n: torch.from_numpy(golden[n])
+    out = orc.gdpa_forward(t("softmax_q"), t("softmax_k"), t("softmax_v"), t("softmax_qo"), t("softmax_ko"),
+                           activation="softmax", qk_scale=None)
+    torch.testing.assert_close(out, t("softmax_out"), atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("act", list(orc.ACTIVATION_IDS))
+def test_activations_match_reference_eager_helper(golden, act):
+    t = lambda n: torch.from_numpy(golden[n])
+    out = orc.gdpa_forward(t("eager_q"), t("eager_k"), t("eager_v"), t("eager_off"), t("eager_off"),
+                           activation=act, qk_scale=None)
+    torch.testing.assert_close(out, t(f"eager_out_{act}"), atol=1e-5, rtol=1e-5)
+
+
+def test_scale_is_applied_after_the_activation(golden):
+    t = lambda n: torch.from_numpy(golden[n])
+    base = t("eager_out_gelu_approx")
+    out = orc.gdpa_forward(t("eager_q"), t("eager_k"), t("eager_v"), t("eager_off"), t("eager_off"),
+                           activation="gelu_approx", qk_scale=0.125)
+    torch.testing.assert_close(out, base * 0.125, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("act", ["raw", "gelu", "gelu_approx", "leaky_relu", "relu", "silu", "hardswish", "relu_square"])
+def test_autograd_matches_closed_form_derivatives(act):
+    rng = np.random.default_rng(7)
+    lq, lk = rng.integers(1, 30, 4), rng.integers(1, 30, 4)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]))
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(int(qo[-1]), 2, 8, generator=g, dtype=torch.float64)
+    k = torch.randn(int(ko[-1]), 2, 8, generator=g, dtype=torch.float64)
+    v = torch.randn(int(ko[-1]), 2, 8, generator=g, dtype=torch.float64)
+    do = torch.randn(int(qo[-1]), 2, 8, generator=g, dtype=torch.float64)
+    _, dq, dk, dv = orc.gdpa_forward_backward(q, k, v, qo, ko, do, act, 0.3)
+    dq2, dk2, dv2 = orc.gdpa_backward_formulas(q, k, v, qo, ko, do, act, 0.3)
+    for a, b in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        torch.testing.assert_close(a, b, atol=2e-4, rtol=2e-4)
+
+
+def test_empty_sequences_and_unknown_activation():
+    qo = torch.tensor([0, 0, 3, 3])
+    ko = torch.tensor([0, 2, 2, 5])
+    q, k, v = torch.randn(3, 1, 4), torch.randn(5, 1, 4), torch.randn(5, 1, 4)
+    out = orc.gdpa_forward(q, k, v, qo, ko, "relu", 1.0)
+    assert torch.equal(out, torch.zeros_like(out))  # the only non-empty Q has an empty KV
+    with pytest.raises(ValueError):
+        orc.gdpa_forward(q, k, v, qo, ko, "tanh", 1.0)
+
+
+def test_useful_flops_formula():
+    assert orc.useful_flops([2, 3], [5, 7], 4, 128, "fwd") == 4 * 4 * 128 * 31
+    assert orc.useful_flops([2, 3], [5, 7], 4, 128, "fwd_bwd") == 14 * 4 * 128 * 31
