@@ -1,0 +1,277 @@
+// C-ABI entry points of libgdpa_b200.so (declared in include/gdpa_b200.h): argument checks,
+// TMA tensor-map encoding, kernel selection and launch.  Nothing here allocates device memory or
+// synchronises a stream.
+#include <atomic>
+#include <cstring>
+
+#include "../../include/gdpa_b200.h"
+#include "gdpa_common.cuh"
+#include "gdpa_launch.h"
+
+namespace gdpa {
+namespace {
+
+std::atomic<long long> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library does not
+// link against libcuda.  The result is immutable once set.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+};
+
+// Immutable per-device attributes, read once per device.
+int device_info(DeviceInfo* out) {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int> ready[kMaxDev];
+  static DeviceInfo info[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return GDPA_ERR_DEVICE;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    DeviceInfo d;
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return GDPA_ERR_DEVICE;
+    if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return GDPA_ERR_DEVICE;
+    info[dev] = d;  // racing writers store identical values
+    ready[dev].store(1, std::memory_order_release);
+  }
+  *out = info[dev];
+  return out->cc_major == 10 ? GDPA_OK : GDPA_ERR_DEVICE;
+}
+
+// Tensor map over a [rows, heads, head_dim] row-major tensor; a box is `box_rows` rows of one
+// head by `box_cols` elements, stored with the 128-byte swizzle (box_cols * elem_bytes == 128)
+// or unswizzled.
+int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
+              int head_dim, int box_cols, int box_rows, bool swizzle128) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return GDPA_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
+                        static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * elem_bytes,
+                           static_cast<cuuint64_t>(head_dim) * heads * elem_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), 1u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
+}
+
+template <class P>
+int check_common(const P* p) {
+  if (p == nullptr || p->struct_size != sizeof(P)) return GDPA_ERR_BAD_ARG;
+  if (p->batch < 0 || p->heads <= 0 || p->total_q < 0 || p->total_kv < 0) return GDPA_ERR_BAD_ARG;
+  if (p->max_seq_len_q < 0 || p->max_seq_len_kv < 0) return GDPA_ERR_BAD_ARG;
+  if (p->head_dim != 64 && p->head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM;
+  if (p->q_offsets == nullptr || p->kv_offsets == nullptr || p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
+  // TMA coordinates are 32-bit row indices.
+  if (p->total_q >= (1ll << 31) || p->total_kv >= (1ll << 31)) return GDPA_ERR_BAD_ARG;
+  return GDPA_OK;
+}
+
+}  // namespace
+}  // namespace gdpa
+
+using namespace gdpa;
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+const char* gdpa_strerror(int code) {
+  switch (code) {
+    case GDPA_OK: return "ok";
+    case GDPA_ERR_BAD_ARG: return "bad argument (null pointer, negative size or struct_size mismatch)";
+    case GDPA_ERR_UNSUPPORTED_DIM: return "unsupported head_dim (supported: 64, 128)";
+    case GDPA_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    case GDPA_ERR_UNSUPPORTED_ACT: return "unsupported activation for this entry point";
+    case GDPA_ERR_MISALIGNED: return "tensor base address is not 16-byte aligned";
+    case GDPA_ERR_LAUNCH: return "kernel launch failed";
+    case GDPA_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
+    case GDPA_ERR_CAPACITY: return "schedule buffer too small";
+    case GDPA_ERR_DEVICE: return "current device is not a compute-capability 10.x GPU";
+    default: return "unknown error code";
+  }
+}
+
+int32_t gdpa_version(void) { return 100; }
+
+int64_t gdpa_launch_count(void) { return g_launches.load(); }
+
+size_t gdpa_schedule_bytes(int32_t mode, int64_t total_rows, int32_t batch, int32_t heads) {
+  if (total_rows < 0 || batch < 0 || heads <= 0) return 0;
+  const int64_t tile = (mode == GDPA_SCHED_FWD) ? kFwdQBlock : kTile;
+  const int64_t items = static_cast<int64_t>(heads) * (total_rows / tile + batch);
+  return static_cast<size_t>(kSchedHeaderInts * 4 + 16 * (items > 0 ? items : 1));
+}
+
+size_t gdpa_bwd_workspace_bytes(int64_t total_q, int32_t heads, int32_t head_dim) {
+  if (total_q < 0 || heads <= 0 || head_dim <= 0) return 0;
+  return static_cast<size_t>(total_q) * heads * head_dim * sizeof(float);
+}
+
+int gdpa_build_schedule(const GdpaSchedParams* p, gdpa_stream_t stream) {
+  if (p == nullptr || p->struct_size != sizeof(GdpaSchedParams)) return GDPA_ERR_BAD_ARG;
+  if (p->batch < 0 || p->heads <= 0 || p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->mode != GDPA_SCHED_FWD && p->mode != GDPA_SCHED_BWD) return GDPA_ERR_BAD_ARG;
+  if (p->batch > 0 && (p->q_offsets == nullptr || p->kv_offsets == nullptr)) return GDPA_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(p->schedule) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  if (p->schedule_bytes < kSchedHeaderInts * 4 + 16) return GDPA_ERR_CAPACITY;
+  SchedArgs a;
+  a.q_off = p->q_offsets;
+  a.kv_off = p->kv_offsets;
+  a.off64 = p->offsets_are_int64;
+  a.batch = p->batch;
+  a.heads = p->heads;
+  a.max_q = p->max_seq_len_q;
+  a.max_kv = p->max_seq_len_kv;
+  a.mode = p->mode;
+  a.sched = static_cast<int*>(p->schedule);
+  a.capacity_items = (p->schedule_bytes - kSchedHeaderInts * 4) / 16;
+  int rc = launch_build_schedule(a, static_cast<cudaStream_t>(stream));
+  if (rc == 0) g_launches.fetch_add(1);
+  return rc;
+}
+
+static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
+  int rc = check_common(p);
+  if (rc != GDPA_OK) return rc;
+  if (p->dtype != (fp8 ? GDPA_DTYPE_FP8_E4M3 : GDPA_DTYPE_BF16)) return GDPA_ERR_UNSUPPORTED_DTYPE;
+  const int act = act_class_from_id(p->activation);
+  if (act < 0) return GDPA_ERR_UNSUPPORTED_ACT;
+  if (p->total_q == 0 || p->batch == 0) return GDPA_OK;
+  if (p->q == nullptr || p->o == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->total_kv > 0 && (p->k == nullptr || p->v == nullptr)) return GDPA_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(p->o) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  if (fp8 && (p->q_scales == nullptr || p->k_scales == nullptr || p->v_scales == nullptr ||
+              p->q_block_offsets == nullptr || p->kv_block_offsets == nullptr))
+    return GDPA_ERR_BAD_ARG;
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc != GDPA_OK) return rc;
+
+  FwdLaunch l;
+  std::memset(&l, 0, sizeof(l));
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int eb = fp8 ? 1 : 2;
+  const int box_cols = 128 / eb;
+  // An empty K/V still needs valid maps for the kernel parameters: point them at Q.
+  const void* kp = p->total_kv > 0 ? p->k : p->q;
+  const void* vp = p->total_kv > 0 ? p->v : p->q;
+  const long long kv_rows = p->total_kv > 0 ? p->total_kv : p->total_q;
+  if ((rc = make_tmap(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  l.args.o = static_cast<__nv_bfloat16*>(p->o);
+  l.args.q_off = p->q_offsets;
+  l.args.kv_off = p->kv_offsets;
+  l.args.off64 = p->offsets_are_int64;
+  l.args.heads = p->heads;
+  l.args.max_q = p->max_seq_len_q;
+  l.args.max_kv = p->max_seq_len_kv;
+  l.args.scale = p->qk_scale;
+  l.args.sched = static_cast<const int*>(p->schedule);
+  l.args.status = p->status;
+  l.args.q_scales = p->q_scales;
+  l.args.k_scales = p->k_scales;
+  l.args.v_scales = p->v_scales;
+  l.args.q_blk_off = p->q_block_offsets;
+  l.args.kv_blk_off = p->kv_block_offsets;
+  l.grid = di.sm_count;
+  l.stream = static_cast<cudaStream_t>(stream);
+  if (fp8) {
+    rc = launch_fwd_fp8(l, p->head_dim, act);
+  } else if (act == ACT_SOFTMAX) {
+    rc = launch_fwd_softmax_bf16(l, p->head_dim);
+  } else {
+    rc = launch_fwd_bf16(l, p->head_dim, act);
+  }
+  if (rc == 0) g_launches.fetch_add(1);
+  return rc;
+}
+
+int gdpa_fwd(const GdpaFwdParams* p, gdpa_stream_t stream) { return fwd_common(p, stream, false); }
+
+int gdpa_fwd_fp8(const GdpaFwdParams* p, gdpa_stream_t stream) { return fwd_common(p, stream, true); }
+
+int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
+  int rc = check_common(p);
+  if (rc != GDPA_OK) return rc;
+  if (p->dtype != GDPA_DTYPE_BF16) return GDPA_ERR_UNSUPPORTED_DTYPE;
+  const int act = act_class_from_id(p->activation);
+  if (act < 0 || act == ACT_SOFTMAX) return GDPA_ERR_UNSUPPORTED_ACT;
+  if (p->batch == 0 || (p->total_q == 0 && p->total_kv == 0)) return GDPA_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t elems_q = static_cast<size_t>(p->total_q) * p->heads * p->head_dim;
+  const size_t elems_kv = static_cast<size_t>(p->total_kv) * p->heads * p->head_dim;
+  if (p->total_q == 0) {
+    // No query rows: dK = dV = 0.
+    if (p->dk == nullptr || p->dv == nullptr) return GDPA_ERR_BAD_ARG;
+    if (cudaMemsetAsync(p->dk, 0, elems_kv * 2, st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+    if (cudaMemsetAsync(p->dv, 0, elems_kv * 2, st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+    return GDPA_OK;
+  }
+  if (p->q == nullptr || p->d_o == nullptr || p->dq == nullptr || p->dq_accum == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->total_kv == 0) {
+    // No key rows: dQ = 0.
+    if (cudaMemsetAsync(p->dq, 0, elems_q * 2, st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+    return GDPA_OK;
+  }
+  if (p->k == nullptr || p->v == nullptr || p->dk == nullptr || p->dv == nullptr) return GDPA_ERR_BAD_ARG;
+  if (((reinterpret_cast<uintptr_t>(p->dk) | reinterpret_cast<uintptr_t>(p->dv) | reinterpret_cast<uintptr_t>(p->dq)) & 15u) != 0)
+    return GDPA_ERR_MISALIGNED;
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc != GDPA_OK) return rc;
+
+  BwdLaunch l;
+  std::memset(&l, 0, sizeof(l));
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if ((rc = make_tmap(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  // fp32 dQ accumulator, reduced into by 32-column x 128-row unswizzled boxes.
+  if ((rc = make_tmap(&l.tm_dq, p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
+                      kTile, false)) != GDPA_OK)
+    return rc;
+  l.args.dk = static_cast<__nv_bfloat16*>(p->dk);
+  l.args.dv = static_cast<__nv_bfloat16*>(p->dv);
+  l.args.dq_accum = static_cast<float*>(p->dq_accum);
+  l.args.q_off = p->q_offsets;
+  l.args.kv_off = p->kv_offsets;
+  l.args.off64 = p->offsets_are_int64;
+  l.args.heads = p->heads;
+  l.args.max_q = p->max_seq_len_q;
+  l.args.max_kv = p->max_seq_len_kv;
+  l.args.scale = p->qk_scale;
+  l.args.sched = static_cast<const int*>(p->schedule);
+  l.args.status = p->status;
+  l.grid = di.sm_count;
+  l.stream = st;
+  if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+  rc = launch_bwd_bf16(l, p->head_dim, act);
+  if (rc != 0) return rc;
+  rc = launch_dq_convert(static_cast<const float*>(p->dq_accum), static_cast<__nv_bfloat16*>(p->dq),
+                         static_cast<long long>(elems_q), st);
+  if (rc == 0) g_launches.fetch_add(2);
+  return rc;
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,165 @@
+// Definitions shared by the GDPA schedule builder, the forward and the backward kernels.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace gdpa {
+
+constexpr int kTile = 128;          // rows of one Q tile / KV tile
+constexpr int kFwdQBlock = 256;     // Q rows of one forward work item (two Q tiles)
+constexpr int kSchedHeaderInts = 4; // schedule buffer: int32 header, then int4 work items
+
+// Activation classes the kernels are specialised on (several reference names share one class).
+enum ActClass : int {
+  ACT_RAW = 0,
+  ACT_GELU_ERF = 1,
+  ACT_GELU_TANH = 2,
+  ACT_LEAKY_RELU = 3,
+  ACT_RELU = 4,
+  ACT_SILU = 5,
+  ACT_HARDSWISH = 6,
+  ACT_RELU_SQUARE = 7,
+  ACT_SOFTMAX = 8,
+  ACT_NUM_CLASSES = 9
+};
+
+__host__ __device__ inline int act_class_from_id(int id) {
+  switch (id) {
+    case 0: return ACT_RAW;
+    case 1: return ACT_GELU_ERF;
+    case 2: case 3: case 6: case 11: return ACT_GELU_TANH;
+    case 4: return ACT_LEAKY_RELU;
+    case 5: return ACT_RELU;
+    case 7: case 8: return ACT_SILU;
+    case 9: return ACT_HARDSWISH;
+    case 10: return ACT_RELU_SQUARE;
+    case 100: return ACT_SOFTMAX;
+    default: return -1;
+  }
+}
+
+__device__ __forceinline__ long long load_offset(const void* p, int i, int is64) {
+  return is64 ? static_cast<const long long*>(p)[i] : static_cast<long long>(static_cast<const int*>(p)[i]);
+}
+
+// One work item of a schedule, with the sequence geometry it refers to.
+struct Work {
+  int b, h, blk;
+  long long q_start, kv_start;
+  int lq, lkv;
+};
+
+__device__ __forceinline__ Work load_work(const int* sched, int idx, const void* q_off, const void* kv_off, int is64,
+                                          int max_q, int max_kv) {
+  const int4 it = reinterpret_cast<const int4*>(sched + kSchedHeaderInts)[idx];
+  Work w;
+  w.b = it.x;
+  w.h = it.y;
+  w.blk = it.z;
+  w.q_start = load_offset(q_off, w.b, is64);
+  w.kv_start = load_offset(kv_off, w.b, is64);
+  long long lq = load_offset(q_off, w.b + 1, is64) - w.q_start;
+  long long lkv = load_offset(kv_off, w.b + 1, is64) - w.kv_start;
+  w.lq = static_cast<int>(lq < max_q ? lq : max_q);
+  w.lkv = static_cast<int>(lkv < max_kv ? lkv : max_kv);
+  if (w.lq < 0) w.lq = 0;
+  if (w.lkv < 0) w.lkv = 0;
+  return w;
+}
+
+// Persistent CTAs walk the longest-first list in a zigzag: round r gives CTA c the item
+// r*G + c on even rounds and r*G + (G-1-c) on odd rounds, so the CTA that drew the longest item of
+// one round draws the shortest of the next.
+struct WorkWalker {
+  int round, grid, cta, count;
+  __device__ WorkWalker(int count_) : round(0), grid(gridDim.x), cta(blockIdx.x), count(count_) {}
+  __device__ __forceinline__ bool next(int& idx) {
+    idx = round * grid + ((round & 1) ? (grid - 1 - cta) : cta);
+    ++round;
+    return idx < count;
+  }
+};
+
+// act(x) * scale for the elementwise activation classes.  `hscale` = 0.5 * scale.
+template <int ACT>
+__device__ __forceinline__ float act_scaled(float x, float scale, float hscale) {
+  if constexpr (ACT == ACT_RAW) {
+    return x * scale;
+  } else if constexpr (ACT == ACT_RELU) {
+    return fmaxf(x, 0.f) * scale;
+  } else if constexpr (ACT == ACT_LEAKY_RELU) {
+    return (x > 0.f ? x : 0.01f * x) * scale;
+  } else if constexpr (ACT == ACT_RELU_SQUARE) {
+    float r = fmaxf(x, 0.f);
+    return r * r * scale;
+  } else if constexpr (ACT == ACT_HARDSWISH) {
+    float r = fminf(fmaxf(x + 3.f, 0.f), 6.f);
+    return x * r * (scale * (1.f / 6.f));
+  } else if constexpr (ACT == ACT_GELU_ERF) {
+    float xs = x * hscale;
+    return fmaf(xs, erff(x * 0.70710678118654752f), xs);
+  } else if constexpr (ACT == ACT_GELU_TANH) {
+    // 0.5 x (1 + tanh(sqrt(2/pi) x (1 + 0.044715 x^2)))
+    float x2 = x * x;
+    float inner = fmaf(x2, 0.7978845608028654f * 0.044715f, 0.7978845608028654f);
+    float t = tanh_approx(x * inner);
+    float xs = x * hscale;
+    return fmaf(xs, t, xs);
+  } else if constexpr (ACT == ACT_SILU) {
+    // x sigmoid(x) = 0.5 x (1 + tanh(x / 2))
+    float t = tanh_approx(0.5f * x);
+    float xs = x * hscale;
+    return fmaf(xs, t, xs);
+  } else {
+    return x;
+  }
+}
+
+// act(x) and act'(x), both already multiplied by `scale`.
+template <int ACT>
+__device__ __forceinline__ void act_and_grad_scaled(float x, float scale, float hscale, float& p, float& g) {
+  if constexpr (ACT == ACT_RAW) {
+    p = x * scale;
+    g = scale;
+  } else if constexpr (ACT == ACT_RELU) {
+    p = fmaxf(x, 0.f) * scale;
+    g = x > 0.f ? scale : 0.f;
+  } else if constexpr (ACT == ACT_LEAKY_RELU) {
+    p = (x > 0.f ? x : 0.01f * x) * scale;
+    g = x > 0.f ? scale : 0.01f * scale;
+  } else if constexpr (ACT == ACT_RELU_SQUARE) {
+    float r = fmaxf(x, 0.f);
+    p = r * r * scale;
+    g = 2.f * r * scale;
+  } else if constexpr (ACT == ACT_HARDSWISH) {
+    float r = fminf(fmaxf(x + 3.f, 0.f), 6.f);
+    p = x * r * (scale * (1.f / 6.f));
+    g = x < -3.f ? 0.f : (x > 3.f ? scale : fmaf(x, 2.f, 3.f) * (scale * (1.f / 6.f)));
+  } else if constexpr (ACT == ACT_GELU_ERF) {
+    float cdf = fmaf(0.5f, erff(x * 0.70710678118654752f), 0.5f);
+    float pdf = __expf(-0.5f * x * x) * 0.3989422804014327f;
+    p = x * cdf * scale;
+    g = fmaf(x, pdf, cdf) * scale;
+  } else if constexpr (ACT == ACT_GELU_TANH) {
+    // p = 0.5 x (1 + t);  p' = 0.5 (1 + t) + 0.5 x (1 - t^2) c0 (1 + 3 c1 x^2)
+    constexpr float c0 = 0.7978845608028654f, c1 = 0.044715f;
+    float x2 = x * x;
+    float t = tanh_approx(x * fmaf(x2, c0 * c1, c0));
+    float xs = x * hscale;
+    p = fmaf(xs, t, xs);
+    float du = fmaf(x2, 3.f * c0 * c1, c0);
+    float sech2 = fmaf(-t, t, 1.f);
+    g = fmaf(xs * sech2, du, fmaf(hscale, t, hscale));
+  } else if constexpr (ACT == ACT_SILU) {
+    // sg = 0.5 (1 + tanh(x/2));  p = x sg;  p' = sg (1 + x (1 - sg))
+    float t = tanh_approx(0.5f * x);
+    float sg = fmaf(0.5f, t, 0.5f);
+    p = x * sg * scale;
+    g = sg * fmaf(x, 1.f - sg, 1.f) * scale;
+  } else {
+    p = x;
+    g = 1.f;
+  }
+}
+
+}  // namespace gdpa

@@ -1,0 +1,376 @@
+// GDPA forward for sm_100a:  O = cast(act(Q K^T) * scale) V  over a jagged batch.
+//
+// One persistent CTA per SM walks a longest-first list of work items (sequence, head, 256-row
+// Q block).  A work item keeps two 128-row Q tiles resident in shared memory and streams the
+// sequence's K and V tiles through a shared-memory ring.  Roles (14 warps):
+//
+//   warps 0-3   activation group 0: S0 (TMEM) -> registers -> act * scale -> bf16 P0 (TMEM)
+//   warps 4-7   activation group 1: same for S1
+//   warps 8-11  epilogue: O0 / O1 (TMEM) -> registers -> bf16 -> global
+//   warp  12    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
+//               O_s += P_s V (A operand P read from TMEM)
+//   warp  13    TMA loader (one lane)
+//
+// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).  P_s (bf16, two
+// values per column) overwrites the first 64 columns of S_s once those have been read.
+// While one activation group works on its S tile the tensor cores run the other group's P V and
+// next Q K^T, so activation and MMA overlap.
+//
+// Rows of a tile that lie beyond the end of a sequence hold other sequences' tokens (or zeros
+// past the end of the tensor): S columns beyond the KV length are set to zero before the
+// activation (act(0) = 0 for every supported activation), Q rows beyond the Q length are
+// computed and never stored.
+#include "gdpa_common.cuh"
+#include "gdpa_launch.h"
+
+namespace gdpa {
+
+namespace {
+
+constexpr int kFwdThreads = 14 * 32;
+constexpr int kMmaWarp = 12;
+constexpr int kLoadWarp = 13;
+constexpr int kKvStages = 4;
+
+// Barrier indices inside the shared barrier array.
+enum FwdBar : int {
+  B_Q_FULL = 0,                        // [2] TMA -> MMA
+  B_Q_EMPTY = 2,                       // [2] MMA commit -> TMA
+  B_KV_FULL = 4,                       // [kKvStages]
+  B_KV_EMPTY = 4 + kKvStages,          // [kKvStages]
+  B_S_FULL = 4 + 2 * kKvStages,        // [2] MMA commit -> activation group
+  B_P_FULL = 6 + 2 * kKvStages,        // [2] activation group (128 arrivals) -> MMA
+  B_O_FULL = 8 + 2 * kKvStages,        // [2] MMA commit -> epilogue
+  B_O_EMPTY = 10 + 2 * kKvStages,      // [2] epilogue (128 arrivals) -> MMA
+  B_COUNT = 12 + 2 * kKvStages
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;       // one 128 x D bf16 tile
+  static constexpr int kHalfBytes = kTile * 64 * 2;      // one 128 x 64 swizzled box
+  static constexpr int kQOff = 0;
+  static constexpr int kKvOff = 2 * kTileBytes;
+  static constexpr int kBarOff = kKvOff + kKvStages * kTileBytes;
+  static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
+  static constexpr int kAbortOff = kTmemPtrOff + 4;
+  static constexpr int kBytes = kAbortOff + 4;
+  static constexpr int kDynBytes = kBytes + 1024;        // slack to align the base to 1024 bytes
+};
+
+#define GDPA_WAIT(bar_idx, parity, role)                                                                   \
+  if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
+    goto role_done;
+
+template <int D, int ACT>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
+  using L = FwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOff;
+  volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < B_COUNT; ++i) {
+      const bool many = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2);
+      mbar_init(bar_base + 8u * i, many ? 128u : 1u);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_base + L::kTmemPtrOff, 512);
+    tmem_relinquish();
+  }
+  if (warp == kLoadWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+  const int n_items = a.sched[0];
+
+  // QK: A = Q tile (K-major), B = K tile (K-major), M = 128, N = 128.
+  constexpr uint32_t kIdescQK = umma_idesc(1, 1, 0, 0, kTile, kTile);
+  // PV: A = P in TMEM, B = V tile (MN-major: head dim contiguous), M = 128, N = D.
+  constexpr uint32_t kIdescPV = umma_idesc(1, 1, 0, 1, kTile, D);
+
+  if (warp == kLoadWarp) {
+    // ------------------------------------------------------------------ TMA loader
+    if (lane == 0) {
+      uint32_t kv_stage = 0, kv_phase = 0, q_phase[2] = {0, 0};
+      WorkWalker walker(n_items);
+      int idx;
+      while (walker.next(idx)) {
+        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+        const int nkv = (w.lkv + kTile - 1) / kTile;
+        if (nkv == 0) continue;
+        const int q0 = w.blk * kFwdQBlock;
+        const int nst = (w.lq - q0 > kTile) ? 2 : 1;
+        const int q_row = static_cast<int>(w.q_start) + q0;
+        const int kv_row = static_cast<int>(w.kv_start);
+        // Issue order Q0, K0, Q1, V0, K1, V1, ...
+        for (int step = 0; step < 2 * nkv + 2; ++step) {
+          if (step == 0 || step == 2) {
+            const int s = step >> 1;
+            if (s >= nst) continue;
+            GDPA_WAIT(B_Q_EMPTY + s, q_phase[s] ^ 1u, ST_ROLE_LOAD);
+            q_phase[s] ^= 1u;
+            const uint32_t bar = bar_base + 8u * (B_Q_FULL + s);
+            mbar_arrive_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf)
+              tma_load_3d(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, w.h,
+                          q_row + s * kTile);
+          } else {
+            const int t = (step == 1) ? 0 : step - 2;  // 0 = K0, 1 = V0, 2 = K1, ...
+            const int j = t >> 1;
+            const CUtensorMap* tm = (t & 1) ? &tm_v : &tm_k;
+            GDPA_WAIT(B_KV_EMPTY + kv_stage, kv_phase ^ 1u, ST_ROLE_LOAD);
+            const uint32_t bar = bar_base + 8u * (B_KV_FULL + kv_stage);
+            mbar_arrive_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf)
+              tma_load_3d(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar, hf * 64,
+                          w.h, kv_row + j * kTile);
+            if (++kv_stage == kKvStages) {
+              kv_stage = 0;
+              kv_phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t kv_stage = 0, kv_phase = 0;
+      uint32_t q_phase[2] = {0, 0}, p_phase[2] = {0, 0}, o_phase[2] = {0, 0};
+      auto issue_qk = [&](int s, uint32_t k_stage) {
+        const uint32_t a_base = smem_base + L::kQOff + s * L::kTileBytes;
+        const uint32_t b_base = smem_base + L::kKvOff + k_stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+          umma_ss_f16(tmem_base + s * kTile, umma_smem_desc_sw128(a_base + off, 16, 1024),
+                      umma_smem_desc_sw128(b_base + off, 16, 1024), kIdescQK, kk > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int s, uint32_t v_stage, bool accumulate) {
+        const uint32_t b_base = smem_base + L::kKvOff + v_stage * L::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          umma_ts_f16(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8,
+                      umma_smem_desc_sw128(b_base + kk * 2048, L::kHalfBytes, 1024), kIdescPV,
+                      (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      WorkWalker walker(n_items);
+      int idx;
+      while (walker.next(idx)) {
+        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+        const int nkv = (w.lkv + kTile - 1) / kTile;
+        if (nkv == 0) continue;
+        const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
+        // First S tiles: S_s = Q_s K_0^T.
+        {
+          const uint32_t k_stage = kv_stage;
+          for (int s = 0; s < nst; ++s) {
+            GDPA_WAIT(B_Q_FULL + s, q_phase[s], ST_ROLE_MMA);
+            q_phase[s] ^= 1u;
+            if (s == 0) GDPA_WAIT(B_KV_FULL + k_stage, kv_phase, ST_ROLE_MMA);
+            tc_fence_after();
+            issue_qk(s, k_stage);
+            tc_commit(bar_base + 8u * (B_S_FULL + s));
+            if (nkv == 1) tc_commit(bar_base + 8u * (B_Q_EMPTY + s));
+          }
+          tc_commit(bar_base + 8u * (B_KV_EMPTY + k_stage));
+          if (++kv_stage == kKvStages) { kv_stage = 0; kv_phase ^= 1u; }
+        }
+        for (int j = 0; j < nkv; ++j) {
+          const bool more = (j + 1 < nkv);
+          const uint32_t v_stage = kv_stage, v_phase = kv_phase;
+          if (++kv_stage == kKvStages) { kv_stage = 0; kv_phase ^= 1u; }
+          const uint32_t k_stage = kv_stage, k_phase = kv_phase;  // K_{j+1}, valid if more
+          if (more) { if (++kv_stage == kKvStages) { kv_stage = 0; kv_phase ^= 1u; } }
+          GDPA_WAIT(B_KV_FULL + v_stage, v_phase, ST_ROLE_MMA);
+          for (int s = 0; s < nst; ++s) {
+            GDPA_WAIT(B_P_FULL + s, p_phase[s], ST_ROLE_MMA);
+            p_phase[s] ^= 1u;
+            if (j == 0) {
+              GDPA_WAIT(B_O_EMPTY + s, o_phase[s] ^ 1u, ST_ROLE_MMA);
+              o_phase[s] ^= 1u;
+            }
+            tc_fence_after();
+            issue_pv(s, v_stage, j > 0);
+            if (more) {
+              if (s == 0) {
+                GDPA_WAIT(B_KV_FULL + k_stage, k_phase, ST_ROLE_MMA);
+                tc_fence_after();
+              }
+              issue_qk(s, k_stage);
+              tc_commit(bar_base + 8u * (B_S_FULL + s));
+              if (j + 2 == nkv) tc_commit(bar_base + 8u * (B_Q_EMPTY + s));
+            } else {
+              tc_commit(bar_base + 8u * (B_O_FULL + s));
+            }
+          }
+          tc_commit(bar_base + 8u * (B_KV_EMPTY + v_stage));
+          if (more) tc_commit(bar_base + 8u * (B_KV_EMPTY + k_stage));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ activation groups
+    const int s = warp >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_base + s * kTile;
+    const float scale = a.scale, hscale = 0.5f * a.scale;
+    uint32_t s_phase = 0;
+    WorkWalker walker(n_items);
+    int idx;
+    while (walker.next(idx)) {
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const int nkv = (w.lkv + kTile - 1) / kTile;
+      const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
+      if (nkv == 0 || s >= nst) continue;
+      for (int j = 0; j < nkv; ++j) {
+        const int valid = min(kTile, w.lkv - j * kTile);  // valid KV columns of this tile
+        GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+        s_phase ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          uint32_t pk[16];
+          tmem_ld32(s_tmem + c * 32, r);
+          tmem_wait_ld();
+          if (valid >= (c + 1) * 32) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack_bf16x2(act_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale),
+                                  act_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(r[2 * i]) : 0.f;
+              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(r[2 * i + 1]) : 0.f;
+              pk[i] = pack_bf16x2(act_scaled<ACT>(x0, scale, hscale), act_scaled<ACT>(x1, scale, hscale));
+            }
+          }
+          tmem_st16(s_tmem + c * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_base + 8u * (B_P_FULL + s));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 8-11)
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t o_phase[2] = {0, 0};
+    WorkWalker walker(n_items);
+    int idx;
+    while (walker.next(idx)) {
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const int nkv = (w.lkv + kTile - 1) / kTile;
+      const int q0 = w.blk * kFwdQBlock;
+      const int nst = (w.lq - q0 > kTile) ? 2 : 1;
+      for (int s = 0; s < nst; ++s) {
+        const int qr = q0 + s * kTile + row;
+        const bool valid = qr < w.lq;
+        uint4* dst = reinterpret_cast<uint4*>(a.o + ((w.q_start + qr) * a.heads + w.h) * static_cast<long long>(D));
+        if (nkv == 0) {
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          }
+          continue;
+        }
+        GDPA_WAIT(B_O_FULL + s, o_phase[s], ST_ROLE_EPI);
+        o_phase[s] ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_base + 256 + s * kTile + c * 32, r);
+          tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
+          }
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              dst[c * 4 + i] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+role_done:
+  // Teardown: everyone meets here (also after a wait ran out), then the allocating warp frees TMEM.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+#undef GDPA_WAIT
+
+template <int D, int ACT>
+int launch_fwd_inst(const FwdLaunch& l) {
+  using L = FwdSmem<D>;
+  auto kernel = gdpa_fwd_kernel<D, ACT>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
+  if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
+  kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
+  return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
+}
+
+template <int D>
+int launch_fwd_d(const FwdLaunch& l, int act_class) {
+  switch (act_class) {
+    case ACT_RAW: return launch_fwd_inst<D, ACT_RAW>(l);
+    case ACT_GELU_ERF: return launch_fwd_inst<D, ACT_GELU_ERF>(l);
+    case ACT_GELU_TANH: return launch_fwd_inst<D, ACT_GELU_TANH>(l);
+    case ACT_LEAKY_RELU: return launch_fwd_inst<D, ACT_LEAKY_RELU>(l);
+    case ACT_RELU: return launch_fwd_inst<D, ACT_RELU>(l);
+    case ACT_SILU: return launch_fwd_inst<D, ACT_SILU>(l);
+    case ACT_HARDSWISH: return launch_fwd_inst<D, ACT_HARDSWISH>(l);
+    case ACT_RELU_SQUARE: return launch_fwd_inst<D, ACT_RELU_SQUARE>(l);
+    default: return GDPA_ERR_UNSUPPORTED_ACT_;
+  }
+}
+
+}  // namespace
+
+int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class) {
+  if (head_dim == 128) return launch_fwd_d<128>(l, act_class);
+  if (head_dim == 64) return launch_fwd_d<64>(l, act_class);
+  return GDPA_ERR_UNSUPPORTED_DIM_;
+}
+
+}  // namespace gdpa

@@ -1,0 +1,85 @@
+// Internal interface between the C-ABI entry points (gdpa_api.cu) and the kernel translation
+// units.  Plain structs only.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gdpa {
+
+// Internal copies of the public return codes (include/gdpa_b200.h).
+constexpr int GDPA_ERR_UNSUPPORTED_DIM_ = 2;
+constexpr int GDPA_ERR_UNSUPPORTED_ACT_ = 4;
+constexpr int GDPA_ERR_LAUNCH_ = 6;
+
+struct FwdArgs {
+  __nv_bfloat16* o;
+  const void* q_off;
+  const void* kv_off;
+  int off64;
+  int heads;
+  int max_q;
+  int max_kv;
+  float scale;
+  const int* sched;
+  int* status;
+  // FP8 path: per-(128-token block, head) fp32 scales and per-sequence block offsets.
+  const float* q_scales;
+  const float* k_scales;
+  const float* v_scales;
+  const void* q_blk_off;
+  const void* kv_blk_off;
+};
+
+struct FwdLaunch {
+  CUtensorMap tm_q, tm_k, tm_v;
+  FwdArgs args;
+  int grid;
+  cudaStream_t stream;
+};
+
+struct BwdArgs {
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  float* dq_accum;
+  const void* q_off;
+  const void* kv_off;
+  int off64;
+  int heads;
+  int max_q;
+  int max_kv;
+  float scale;
+  const int* sched;
+  int* status;
+};
+
+struct BwdLaunch {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq;
+  BwdArgs args;
+  int grid;
+  cudaStream_t stream;
+};
+
+struct SchedArgs {
+  const void* q_off;
+  const void* kv_off;
+  int off64;
+  int batch;
+  int heads;
+  int max_q;
+  int max_kv;
+  int mode;
+  int* sched;
+  long long capacity_items;
+};
+
+int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class);
+int launch_fwd_softmax_bf16(const FwdLaunch& l, int head_dim);
+int launch_fwd_fp8(const FwdLaunch& l, int head_dim, int act_class);
+int launch_bwd_bf16(const BwdLaunch& l, int head_dim, int act_class);
+int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
+int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
+
+}  // namespace gdpa

@@ -1,0 +1,11 @@
+"""GDPA operator package: drop-in for the reference's ``gdpa`` entry point."""
+from .math import Activation, activation_string_to_int, activation_to_int, int_to_activation  # noqa: F401
+from .ops import (  # noqa: F401
+    expect_contiguous,
+    generalized_dot_product_attention,
+    generalized_dot_product_attention_fp8,
+    kernel_status,
+    quantize_fp8_blockwise,
+)
+from .sharding import plan_token_balanced_shards, shard_jagged  # noqa: F401
+from .workloads import WORKLOADS, make_workload, useful_flops  # noqa: F401

@@ -1,0 +1,144 @@
+"""ctypes binding of libgdpa_b200.so (C ABI declared in include/gdpa_b200.h).
+
+The library is the only compute path of this package: if it is missing or cannot be loaded,
+importing this module raises -- there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libgdpa_b200.so")
+
+# Return codes, activation ids and enums of include/gdpa_b200.h
+GDPA_OK = 0
+GDPA_DTYPE_BF16 = 0
+GDPA_DTYPE_FP8_E4M3 = 1
+GDPA_SCHED_FWD = 0
+GDPA_SCHED_BWD = 1
+GDPA_ACT_SOFTMAX = 100
+
+EXPORTS = (
+    "gdpa_schedule_bytes",
+    "gdpa_build_schedule",
+    "gdpa_fwd",
+    "gdpa_fwd_fp8",
+    "gdpa_bwd_workspace_bytes",
+    "gdpa_bwd",
+    "gdpa_strerror",
+    "gdpa_launch_count",
+    "gdpa_version",
+)
+
+
+class GdpaSchedParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("mode", C.c_int32),
+        ("q_offsets", C.c_void_p),
+        ("kv_offsets", C.c_void_p),
+        ("offsets_are_int64", C.c_int32),
+        ("batch", C.c_int32),
+        ("heads", C.c_int32),
+        ("max_seq_len_q", C.c_int32),
+        ("max_seq_len_kv", C.c_int32),
+        ("reserved", C.c_int32),
+        ("schedule", C.c_void_p),
+        ("schedule_bytes", C.c_int64),
+    ]
+
+
+class GdpaFwdParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("o", C.c_void_p),
+        ("q_offsets", C.c_void_p),
+        ("kv_offsets", C.c_void_p),
+        ("offsets_are_int64", C.c_int32),
+        ("batch", C.c_int32),
+        ("total_q", C.c_int64),
+        ("total_kv", C.c_int64),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("max_seq_len_q", C.c_int32),
+        ("max_seq_len_kv", C.c_int32),
+        ("activation", C.c_int32),
+        ("qk_scale", C.c_float),
+        ("schedule", C.c_void_p),
+        ("status", C.c_void_p),
+        ("q_scales", C.c_void_p),
+        ("k_scales", C.c_void_p),
+        ("v_scales", C.c_void_p),
+        ("q_block_offsets", C.c_void_p),
+        ("kv_block_offsets", C.c_void_p),
+    ]
+
+
+class GdpaBwdParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("d_o", C.c_void_p),
+        ("dq", C.c_void_p),
+        ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("q_offsets", C.c_void_p),
+        ("kv_offsets", C.c_void_p),
+        ("offsets_are_int64", C.c_int32),
+        ("batch", C.c_int32),
+        ("total_q", C.c_int64),
+        ("total_kv", C.c_int64),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("max_seq_len_q", C.c_int32),
+        ("max_seq_len_kv", C.c_int32),
+        ("activation", C.c_int32),
+        ("qk_scale", C.c_float),
+        ("schedule", C.c_void_p),
+        ("dq_accum", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m ads_model_kernel_library_b200.build` "
+            "(needs nvcc); this package has no other compute path"
+        )
+    lib = C.CDLL(LIB_PATH)
+    lib.gdpa_schedule_bytes.restype = C.c_size_t
+    lib.gdpa_schedule_bytes.argtypes = [C.c_int32, C.c_int64, C.c_int32, C.c_int32]
+    lib.gdpa_build_schedule.restype = C.c_int
+    lib.gdpa_build_schedule.argtypes = [C.POINTER(GdpaSchedParams), C.c_void_p]
+    lib.gdpa_fwd.restype = C.c_int
+    lib.gdpa_fwd.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
+    lib.gdpa_fwd_fp8.restype = C.c_int
+    lib.gdpa_fwd_fp8.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
+    lib.gdpa_bwd_workspace_bytes.restype = C.c_size_t
+    lib.gdpa_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32]
+    lib.gdpa_bwd.restype = C.c_int
+    lib.gdpa_bwd.argtypes = [C.POINTER(GdpaBwdParams), C.c_void_p]
+    lib.gdpa_strerror.restype = C.c_char_p
+    lib.gdpa_strerror.argtypes = [C.c_int]
+    lib.gdpa_launch_count.restype = C.c_int64
+    lib.gdpa_launch_count.argtypes = []
+    lib.gdpa_version.restype = C.c_int32
+    lib.gdpa_version.argtypes = []
+    return lib
+
+
+lib = _load()
+
+
+def check(code: int, what: str) -> None:
+    if code != GDPA_OK:
+        raise RuntimeError(f"{what}: {lib.gdpa_strerror(code).decode()} (code {code})")

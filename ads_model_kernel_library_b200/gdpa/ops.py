@@ -1,0 +1,408 @@
+"""Host side of the GDPA operator: the reference's Python entry point, re-implemented over the
+C-ABI kernel library.
+
+``generalized_dot_product_attention`` keeps the name, the positional order and the keyword
+names of the reference function (gdpa/triton/triton_generalized_dot_product_attention.py:4229-4267)
+and is backed by the torch custom op ``gdpa::generalized_dot_product_attention`` with autograd
+registered the same way the reference does it (:3099, :3888-3894).  PyTorch is used for device
+memory and streams only; all arithmetic runs in libgdpa_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import _cabi
+from .math import SOFTMAX_ID, activation_string_to_int
+
+_SUPPORTED_HEAD_DIMS = (64, 128)
+_status_words = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word the kernels write when one of their bounded waits runs out."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = t
+    return t
+
+
+def kernel_status(device=None) -> int:
+    """Read (and clear) the kernels' status word of a device: 0 = every wait completed.
+    Synchronises the device; meant for tests and diagnostics, not for the hot path."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = _status_word(device)
+    v = int(t.item())
+    if v != 0:
+        t.zero_()
+    return v
+
+
+def _stream_ptr() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check_inputs(q, k, v, qo, ko, dtype) -> Tuple[int, int, int]:
+    for name, t in (("query", q), ("key", k), ("value", v)):
+        if t.dim() != 3:
+            raise ValueError(f"{name} must be [total_tokens, H, D], got {tuple(t.shape)}")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: this operator has no CPU path")
+        if t.dtype != dtype:
+            raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    if k.shape != v.shape:
+        raise ValueError("key and value must have the same shape")
+    H, D = q.shape[1], q.shape[2]
+    if k.shape[1] != H or k.shape[2] != D:
+        raise NotImplementedError("query and key/value must have the same number of heads and head_dim")
+    if D not in _SUPPORTED_HEAD_DIMS:
+        raise NotImplementedError(f"head_dim {D} is not supported (supported: {_SUPPORTED_HEAD_DIMS})")
+    for name, t in (("query_offset", qo), ("key_offset", ko)):
+        if t.dim() != 1 or t.numel() < 1:
+            raise ValueError(f"{name} must be a 1-D tensor of batch + 1 entries")
+        if t.dtype not in (torch.int32, torch.int64):
+            raise TypeError(f"{name} must be int32 or int64, got {t.dtype}")
+        if t.device != q.device:
+            raise RuntimeError(f"{name} must be on the same device as query")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    if qo.numel() != ko.numel() or qo.dtype != ko.dtype:
+        raise ValueError("query_offset and key_offset must have the same length and dtype")
+    return qo.numel() - 1, H, D
+
+
+def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, max_q: int, max_kv: int) -> torch.Tensor:
+    nbytes = _cabi.lib.gdpa_schedule_bytes(mode, total_rows, batch, heads)
+    sched = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=qo.device)
+    p = _cabi.GdpaSchedParams()
+    p.struct_size = C.sizeof(_cabi.GdpaSchedParams)
+    p.mode = mode
+    p.q_offsets = qo.data_ptr()
+    p.kv_offsets = ko.data_ptr()
+    p.offsets_are_int64 = int(qo.dtype == torch.int64)
+    p.batch = batch
+    p.heads = heads
+    p.max_seq_len_q = max_q
+    p.max_seq_len_kv = max_kv
+    p.schedule = sched.data_ptr()
+    p.schedule_bytes = sched.numel() * 4
+    _cabi.check(_cabi.lib.gdpa_build_schedule(C.byref(p), _stream_ptr()), "gdpa_build_schedule")
+    return sched
+
+
+def _fill_fwd_params(q, k, v, o, qo, ko, batch, H, D, max_q, max_kv, scale, act_id, sched, dtype_id) -> _cabi.GdpaFwdParams:
+    p = _cabi.GdpaFwdParams()
+    p.struct_size = C.sizeof(_cabi.GdpaFwdParams)
+    p.dtype = dtype_id
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    p.q_offsets, p.kv_offsets = qo.data_ptr(), ko.data_ptr()
+    p.offsets_are_int64 = int(qo.dtype == torch.int64)
+    p.batch = batch
+    p.total_q, p.total_kv = q.shape[0], k.shape[0]
+    p.heads, p.head_dim = H, D
+    p.max_seq_len_q, p.max_seq_len_kv = max_q, max_kv
+    p.activation = act_id
+    p.qk_scale = scale
+    p.schedule = sched.data_ptr()
+    p.status = _status_word(q.device).data_ptr()
+    return p
+
+
+@torch.library.custom_op("gdpa::generalized_dot_product_attention", mutates_args=(), device_types="cuda")
+def _gdpa_forward_op(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: float,
+    activation: int,
+) -> torch.Tensor:
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    with torch.cuda.device(query.device):
+        o = torch.empty_like(query)
+        if query.shape[0] == 0 or batch == 0:
+            return o
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
+                                max_seq_len_q, max_seq_len_kv)
+        p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
+                             max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
+        _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
+    return o
+
+
+@_gdpa_forward_op.register_fake
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+    return torch.empty_like(query)
+
+
+@torch.library.custom_op("gdpa::generalized_dot_product_attention_backward", mutates_args=(), device_types="cuda")
+def _gdpa_backward_op(
+    do: torch.Tensor,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: float,
+    activation: int,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    if activation == SOFTMAX_ID:
+        raise NotImplementedError("the softmax activation has no backward in this library")
+    if do.shape != query.shape or do.dtype != query.dtype:
+        raise ValueError("grad_output must have the shape and dtype of query")
+    do = do.contiguous()
+    with torch.cuda.device(query.device):
+        dq = torch.empty_like(query)
+        dk = torch.empty_like(key)
+        dv = torch.empty_like(value)
+        if batch == 0 or (query.shape[0] == 0 and key.shape[0] == 0):
+            return dq, dk, dv
+        sched = _build_schedule(_cabi.GDPA_SCHED_BWD, query_offset, key_offset, batch, H, key.shape[0],
+                                max_seq_len_q, max_seq_len_kv)
+        acc_bytes = _cabi.lib.gdpa_bwd_workspace_bytes(query.shape[0], H, D)
+        dq_accum = torch.empty(max(acc_bytes // 4, 1), dtype=torch.float32, device=query.device)
+        p = _cabi.GdpaBwdParams()
+        p.struct_size = C.sizeof(_cabi.GdpaBwdParams)
+        p.dtype = _cabi.GDPA_DTYPE_BF16
+        p.q, p.k, p.v, p.d_o = query.data_ptr(), key.data_ptr(), value.data_ptr(), do.data_ptr()
+        p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        p.q_offsets, p.kv_offsets = query_offset.data_ptr(), key_offset.data_ptr()
+        p.offsets_are_int64 = int(query_offset.dtype == torch.int64)
+        p.batch = batch
+        p.total_q, p.total_kv = query.shape[0], key.shape[0]
+        p.heads, p.head_dim = H, D
+        p.max_seq_len_q, p.max_seq_len_kv = max_seq_len_q, max_seq_len_kv
+        p.activation = activation
+        p.qk_scale = qk_scale
+        p.schedule = sched.data_ptr()
+        p.dq_accum = dq_accum.data_ptr()
+        p.status = _status_word(query.device).data_ptr()
+        _cabi.check(_cabi.lib.gdpa_bwd(C.byref(p), _stream_ptr()), "gdpa_bwd")
+    return dq, dk, dv
+
+
+@_gdpa_backward_op.register_fake
+def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+    return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+
+
+def _setup_context(ctx, inputs, output):
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, activation = inputs
+    ctx.save_for_backward(query, key, value, query_offset, key_offset)
+    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation = max_q, max_kv, qk_scale, activation
+
+
+def _backward(ctx, do):
+    query, key, value, query_offset, key_offset = ctx.saved_tensors
+    dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
+        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation
+    )
+    return dq, dk, dv, None, None, None, None, None, None
+
+
+_gdpa_forward_op.register_autograd(_backward, setup_context=_setup_context)
+
+
+@torch.library.custom_op("gdpa::generalized_dot_product_attention_fp8", mutates_args=(), device_types="cuda")
+def _gdpa_forward_fp8_op(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    q_scales: torch.Tensor,
+    k_scales: torch.Tensor,
+    v_scales: torch.Tensor,
+    q_block_offsets: torch.Tensor,
+    kv_block_offsets: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: float,
+    activation: int,
+) -> torch.Tensor:
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.float8_e4m3fn)
+    for name, t in (("q_scales", q_scales), ("k_scales", k_scales), ("v_scales", v_scales)):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.device != query.device:
+            raise ValueError(f"{name} must be a contiguous fp32 tensor on the device of query")
+    for name, t in (("q_block_offsets", q_block_offsets), ("kv_block_offsets", kv_block_offsets)):
+        if t.dtype != query_offset.dtype or t.numel() != batch + 1 or t.device != query.device:
+            raise ValueError(f"{name} must have the dtype and length of the offsets")
+    with torch.cuda.device(query.device):
+        o = torch.empty(query.shape, dtype=torch.bfloat16, device=query.device)
+        if query.shape[0] == 0 or batch == 0:
+            return o
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
+                                max_seq_len_q, max_seq_len_kv)
+        p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
+                             max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_FP8_E4M3)
+        p.q_scales, p.k_scales, p.v_scales = q_scales.data_ptr(), k_scales.data_ptr(), v_scales.data_ptr()
+        p.q_block_offsets, p.kv_block_offsets = q_block_offsets.data_ptr(), kv_block_offsets.data_ptr()
+        _cabi.check(_cabi.lib.gdpa_fwd_fp8(C.byref(p), _stream_ptr()), "gdpa_fwd_fp8")
+    return o
+
+
+@_gdpa_forward_fp8_op.register_fake
+def _(query, key, value, q_scales, k_scales, v_scales, q_block_offsets, kv_block_offsets, query_offset, key_offset,
+      max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+    return torch.empty(query.shape, dtype=torch.bfloat16, device=query.device)
+
+
+def expect_contiguous(x: torch.Tensor) -> torch.Tensor:
+    """Same helper as the reference (gdpa/triton/triton_generalized_dot_product_attention.py:4296)."""
+    return x if x.is_contiguous() else x.contiguous()
+
+
+@torch.fx.wrap
+def generalized_dot_product_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    ad_to_request_offset: Optional[torch.Tensor] = None,
+    attn_mask: Optional[torch.Tensor] = None,
+    attn_offset: Optional[torch.Tensor] = None,
+    is_causal: bool = False,
+    qk_scale: Optional[float] = None,
+    seq_index: Optional[torch.Tensor] = None,
+    allow_tf32: bool = True,
+    output_offset: Optional[torch.Tensor] = None,
+    use_start_end_offsets: bool = False,
+    window_size: Optional[int] = None,
+    broadcast_q: bool = False,
+    activation: str = "raw",
+    enable_persistent: bool = False,
+    enable_tma: bool = False,
+    enable_ws: bool = False,
+    use_dq_atomic_add: bool = False,
+    total_num_objects: Optional[int] = None,
+    ts_encoding_params: Optional[torch.Tensor] = None,
+    ts_event_request_even_params: Optional[torch.Tensor] = None,
+    ts_event_request_log_params: Optional[torch.Tensor] = None,
+    ts_adjacent_event_log_params: Optional[torch.Tensor] = None,
+    ts_encoding_bucket_values: Optional[torch.Tensor] = None,
+    ts_event_request_even_bucket_values: Optional[torch.Tensor] = None,
+    ts_event_request_log_bucket_values: Optional[torch.Tensor] = None,
+    ts_adjacent_event_log_bucket_values: Optional[torch.Tensor] = None,
+    pos_emb_params: Optional[torch.Tensor] = None,
+    pos_emb_bucket_values: Optional[torch.Tensor] = None,
+    bwd_opt_tech: str = "base",
+    ensemble_activation_list: Optional[List[int]] = None,
+) -> torch.Tensor:
+    """Jagged GDPA: for every sequence b and head h, ``O = (act(Q K^T) * qk_scale) V``.
+
+    Same signature as the reference entry point.  ``query`` is ``[total_q, H, D]``, ``key`` and
+    ``value`` are ``[total_kv, H, D]`` (bf16, D in {64, 128}); ``query_offset`` / ``key_offset`` are
+    ``[B + 1]`` int32 or int64 prefix sums.  ``qk_scale=None`` means 1.0, as in the reference
+    (:3148-3149).  ``activation`` is a reference activation name, or ``"softmax"`` (forward only),
+    for which ``qk_scale`` multiplies the scores before the exponential.
+
+    Scheduling knobs of the reference (``seq_index``, ``enable_persistent``, ``enable_tma``,
+    ``enable_ws``, ``use_dq_atomic_add``, ``bwd_opt_tech``, ``allow_tf32``, ``total_num_objects``) are
+    accepted and ignored: scheduling is internal.  Every other non-default option raises, as the
+    reference does for masks and causality (:3138-3139).
+    """
+    if attn_mask is not None:
+        raise NotImplementedError("attn_mask/bias unsupported")
+    if is_causal:
+        raise NotImplementedError("Causal unsupported")
+    unsupported = {
+        "ad_to_request_offset": ad_to_request_offset, "attn_offset": attn_offset, "output_offset": output_offset,
+        "window_size": window_size, "ts_encoding_params": ts_encoding_params,
+        "ts_event_request_even_params": ts_event_request_even_params,
+        "ts_event_request_log_params": ts_event_request_log_params,
+        "ts_adjacent_event_log_params": ts_adjacent_event_log_params,
+        "ts_encoding_bucket_values": ts_encoding_bucket_values,
+        "ts_event_request_even_bucket_values": ts_event_request_even_bucket_values,
+        "ts_event_request_log_bucket_values": ts_event_request_log_bucket_values,
+        "ts_adjacent_event_log_bucket_values": ts_adjacent_event_log_bucket_values,
+        "pos_emb_params": pos_emb_params, "pos_emb_bucket_values": pos_emb_bucket_values,
+        "ensemble_activation_list": ensemble_activation_list,
+    }
+    for name, val in unsupported.items():
+        if val is not None:
+            raise NotImplementedError(f"{name} is not supported by this implementation")
+    if use_start_end_offsets or broadcast_q:
+        raise NotImplementedError("use_start_end_offsets / broadcast_q are not supported by this implementation")
+    if key is None or value is None:
+        raise NotImplementedError("fused QKV / fused KV layouts are not supported by this implementation")
+    act_id = activation_string_to_int(activation)
+    scale = 1.0 if qk_scale is None else float(qk_scale)
+    query = expect_contiguous(query)
+    key = expect_contiguous(key)
+    value = expect_contiguous(value)
+    return torch.ops.gdpa.generalized_dot_product_attention(
+        query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id
+    )
+
+
+def quantize_fp8_blockwise(x: torch.Tensor, offsets: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Quantise a jagged ``[total, H, D]`` tensor to FP8 e4m3 with one fp32 scale per
+    (sequence-local 128-token block, head): ``scale = amax / 448`` over the block.
+
+    Returns ``(x_fp8, scales[num_blocks, H], block_offsets[B + 1])`` where block ``j`` of sequence
+    ``b`` is row ``block_offsets[b] + j`` of ``scales``.  Host-side utility (torch ops, one host
+    read of the offsets); it is the producer of the inputs of
+    :func:`generalized_dot_product_attention_fp8`.
+    """
+    off = offsets.to(torch.int64).cpu()
+    lens = off[1:] - off[:-1]
+    nblk = (lens + 127) // 128
+    blk_off = torch.zeros(off.numel(), dtype=torch.int64)
+    blk_off[1:] = torch.cumsum(nblk, 0)
+    total, H, D = x.shape
+    # block id of every token
+    tok_blk = torch.empty(total, dtype=torch.int64)
+    for b in range(lens.numel()):
+        s, e = int(off[b]), int(off[b + 1])
+        if e > s:
+            tok_blk[s:e] = int(blk_off[b]) + torch.arange(e - s) // 128
+    tok_blk = tok_blk.to(x.device)
+    nb = int(blk_off[-1])
+    amax = torch.zeros(max(nb, 1), H, dtype=torch.float32, device=x.device)
+    xa = x.float().abs().amax(dim=2)
+    amax.index_reduce_(0, tok_blk, xa, "amax", include_self=True)
+    scales = (amax / 448.0).clamp_min(1e-12)
+    x8 = (x.float() / scales[tok_blk].unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return x8, scales.contiguous(), blk_off.to(offsets.dtype).to(x.device)
+
+
+def generalized_dot_product_attention_fp8(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    q_scales: torch.Tensor,
+    k_scales: torch.Tensor,
+    v_scales: torch.Tensor,
+    q_block_offsets: torch.Tensor,
+    kv_block_offsets: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: Optional[float] = None,
+    activation: str = "softmax",
+) -> torch.Tensor:
+    """Low-precision forward: FP8 e4m3 Q/K/V with per-128-token-block fp32 scales, bf16 output.
+    Mirrors the reference's FP8 forward (gdpa/src/interface.py:1053 output dtype rule)."""
+    act_id = activation_string_to_int(activation)
+    scale = 1.0 if qk_scale is None else float(qk_scale)
+    return torch.ops.gdpa.generalized_dot_product_attention_fp8(
+        expect_contiguous(query), expect_contiguous(key), expect_contiguous(value), q_scales, k_scales, v_scales,
+        q_block_offsets, kv_block_offsets, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale,
+        act_id,
+    )

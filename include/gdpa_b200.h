@@ -1,0 +1,206 @@
+/*
+ * gdpa_b200.h -- C ABI of the B200 (sm_100a) GDPA kernel library (libgdpa_b200.so).
+ *
+ * GDPA = Generalized Dot Product Attention over jagged batches: for every sequence b and head h
+ *     S = Q_b,h K_b,h^T            (fp32 accumulate)
+ *     P = act(S) * qk_scale        (elementwise activation, scale AFTER the activation)
+ *     O = cast(P) V_b,h
+ * or, for GDPA_ACT_SOFTMAX, P = softmax(qk_scale * S) with online rescaling.
+ *
+ * The reference library (facebookresearch/ads_model_kernel_library) has no native boundary: its
+ * kernels are Python DSL objects called from Python.  The entry points below are what a binding
+ * for the reference's operator `gdpa::generalized_dot_product_attention` would call; each one
+ * cites the reference interface it replaces (paths are relative to the reference's root).
+ *
+ * Conventions
+ *  - Every pointer in the parameter structs is a DEVICE pointer unless its name ends in `_host`.
+ *  - Q is [total_q, heads, head_dim], K and V are [total_kv, heads, head_dim], row-major and
+ *    contiguous; offsets are [batch + 1] exclusive prefix sums of the sequence lengths, int32 or
+ *    int64 (offsets_are_int64).
+ *  - The library allocates nothing and never synchronises the stream.  Scratch buffers
+ *    (schedule, fp32 dQ accumulator, status word) are supplied by the caller; their sizes come
+ *    from gdpa_schedule_bytes() and gdpa_bwd_workspace_bytes().
+ *  - Entry points return 0 on success or a GDPA_ERR_* code; no C++ exception crosses the
+ *    boundary.  gdpa_strerror() turns a code into text.
+ *  - Every in-kernel wait is bounded.  A wait that runs out writes a non-zero code to
+ *    `status` (if given), the kernel frees its tensor memory and returns; the context stays
+ *    usable.
+ */
+#ifndef GDPA_B200_H_
+#define GDPA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer. */
+typedef void* gdpa_stream_t;
+
+/* Return codes. */
+enum {
+  GDPA_OK = 0,
+  GDPA_ERR_BAD_ARG = 1,        /* null pointer, negative size, struct_size mismatch            */
+  GDPA_ERR_UNSUPPORTED_DIM = 2,/* head_dim not in {64, 128}                                    */
+  GDPA_ERR_UNSUPPORTED_DTYPE = 3,
+  GDPA_ERR_UNSUPPORTED_ACT = 4,
+  GDPA_ERR_MISALIGNED = 5,     /* a tensor base is not 16-byte aligned                         */
+  GDPA_ERR_LAUNCH = 6,         /* cudaGetLastError() after a launch was not cudaSuccess        */
+  GDPA_ERR_DRIVER = 7,         /* tensor-map encoding entry point unavailable or failed        */
+  GDPA_ERR_CAPACITY = 8,       /* schedule buffer too small for this batch                     */
+  GDPA_ERR_DEVICE = 9          /* current device is not compute capability 10.x               */
+};
+
+/* Activation ids.  0..11 are the reference's enumeration order
+ * (gdpa/triton/math.py:43-55, :77-78); 100 is this library's name for the behaviour of the
+ * reference's CPU kernel (softmax, gdpa/triton/triton_generalized_dot_product_attention.py:3973). */
+enum {
+  GDPA_ACT_RAW = 0,
+  GDPA_ACT_GELU = 1,            /* exact erf GELU */
+  GDPA_ACT_GELU_APPROX = 2,     /* tanh GELU      */
+  GDPA_ACT_FAST_GELU = 3,       /* tanh GELU      */
+  GDPA_ACT_LEAKY_RELU = 4,      /* slope 0.01     */
+  GDPA_ACT_RELU = 5,
+  GDPA_ACT_FAST_GELU_BF16 = 6,  /* tanh GELU      */
+  GDPA_ACT_SILU = 7,
+  GDPA_ACT_FAST_SILU = 8,
+  GDPA_ACT_HARDSWISH = 9,
+  GDPA_ACT_RELU_SQUARE = 10,
+  GDPA_ACT_FAST_GELU_TAYLOR = 11, /* evaluated as tanh GELU, as the reference's eager table does */
+  GDPA_ACT_SOFTMAX = 100
+};
+
+enum { GDPA_DTYPE_BF16 = 0, GDPA_DTYPE_FP8_E4M3 = 1 };
+
+/* Which pass a schedule is for. */
+enum {
+  GDPA_SCHED_FWD = 0, /* one work item per (sequence, head, 256-row Q block)  */
+  GDPA_SCHED_BWD = 1  /* one work item per (sequence, head, 128-row KV tile)  */
+};
+
+/* ---------------------------------------------------------------------------------------------
+ * Work schedule: the list of tiles the persistent kernels walk, longest first.
+ * Replaces precompute_for_varline_load_balancing (gdpa/src/interface.py:219-325), which builds
+ * the same kind of list with torch ops and host synchronisations; this one is built on the device
+ * without a host sync.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct GdpaSchedParams {
+  uint32_t struct_size;       /* sizeof(GdpaSchedParams) */
+  int32_t mode;               /* GDPA_SCHED_FWD or GDPA_SCHED_BWD */
+  const void* q_offsets;      /* [batch + 1] */
+  const void* kv_offsets;     /* [batch + 1] */
+  int32_t offsets_are_int64;
+  int32_t batch;
+  int32_t heads;
+  int32_t max_seq_len_q;      /* lengths are clamped to these, as the reference does          */
+  int32_t max_seq_len_kv;     /*   (gdpa/triton/triton_generalized_dot_product_attention.py:599-624) */
+  int32_t reserved;
+  void* schedule;             /* out: gdpa_schedule_bytes() bytes, 16-byte aligned             */
+  int64_t schedule_bytes;     /* size of that buffer                                           */
+} GdpaSchedParams;
+
+/* Bytes needed for a schedule of the given pass.  total_rows is total_q for GDPA_SCHED_FWD and
+ * total_kv for GDPA_SCHED_BWD.  Pure host arithmetic. */
+size_t gdpa_schedule_bytes(int32_t mode, int64_t total_rows, int32_t batch, int32_t heads);
+
+/* Build the schedule on `stream`.  No host synchronisation. */
+int gdpa_build_schedule(const GdpaSchedParams* params, gdpa_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Forward.  Replaces the launch half of torch.ops.gdpa.generalized_dot_product_attention
+ * (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335) and of _flash_attn_fwd
+ * (gdpa/src/interface.py:931-1254): one persistent tcgen05 kernel.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct GdpaFwdParams {
+  uint32_t struct_size;       /* sizeof(GdpaFwdParams) */
+  int32_t dtype;              /* GDPA_DTYPE_BF16 */
+  const void* q;              /* [total_q,  heads, head_dim] */
+  const void* k;              /* [total_kv, heads, head_dim] */
+  const void* v;              /* [total_kv, heads, head_dim] */
+  void* o;                    /* out [total_q, heads, head_dim], bf16 */
+  const void* q_offsets;
+  const void* kv_offsets;
+  int32_t offsets_are_int64;
+  int32_t batch;
+  int64_t total_q;
+  int64_t total_kv;
+  int32_t heads;
+  int32_t head_dim;           /* 64 or 128 */
+  int32_t max_seq_len_q;
+  int32_t max_seq_len_kv;
+  int32_t activation;         /* GDPA_ACT_* */
+  float qk_scale;             /* multiplies act(S); for softmax multiplies S before exp */
+  const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_FWD) */
+  int32_t* status;            /* optional device int32, written non-zero if a wait ran out */
+  /* FP8 path only (gdpa_fwd_fp8): one fp32 scale per (sequence-local 128-token block, head),
+   * laid out [number of blocks over the batch, heads]; block b of sequence s sits at row
+   * block_offsets[s] + b where block_offsets is the exclusive prefix sum of ceil(len / 128). */
+  const float* q_scales;
+  const float* k_scales;
+  const float* v_scales;
+  const void* q_block_offsets;  /* [batch + 1], same integer type as the offsets */
+  const void* kv_block_offsets; /* [batch + 1] */
+} GdpaFwdParams;
+
+int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
+
+/* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16.
+ * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule
+ * gdpa/src/interface.py:1053). */
+int gdpa_fwd_fp8(const GdpaFwdParams* params, gdpa_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Backward.  Replaces torch.ops.gdpa.generalized_dot_product_attention_backward
+ * (gdpa/triton/triton_generalized_dot_product_attention.py:3461-3788) and _flash_attn_bwd
+ * (gdpa/src/interface.py:1257-1685): S and P are recomputed, dQ, dK, dV come out of one
+ * persistent kernel; dQ is accumulated in fp32 (the reference reduces into bf16,
+ * gdpa/src/flash_bwd_sm100.py:2267-2287) and rounded once by a second, bandwidth-bound kernel.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct GdpaBwdParams {
+  uint32_t struct_size;       /* sizeof(GdpaBwdParams) */
+  int32_t dtype;              /* GDPA_DTYPE_BF16 */
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* d_o;            /* [total_q, heads, head_dim] gradient of O */
+  void* dq;                   /* out [total_q,  heads, head_dim] bf16 */
+  void* dk;                   /* out [total_kv, heads, head_dim] bf16 */
+  void* dv;                   /* out [total_kv, heads, head_dim] bf16 */
+  const void* q_offsets;
+  const void* kv_offsets;
+  int32_t offsets_are_int64;
+  int32_t batch;
+  int64_t total_q;
+  int64_t total_kv;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t max_seq_len_q;
+  int32_t max_seq_len_kv;
+  int32_t activation;
+  float qk_scale;
+  const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_BWD) */
+  void* dq_accum;             /* scratch: gdpa_bwd_workspace_bytes() bytes; zeroed by gdpa_bwd */
+  int32_t* status;
+} GdpaBwdParams;
+
+/* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */
+size_t gdpa_bwd_workspace_bytes(int64_t total_q, int32_t heads, int32_t head_dim);
+
+int gdpa_bwd(const GdpaBwdParams* params, gdpa_stream_t stream);
+
+/* Text for a return code (static storage). */
+const char* gdpa_strerror(int code);
+
+/* Number of kernels launched by this library in this process so far (all entry points).
+ * Used by benchmarks to report how many of this library's kernels ran in a timed region. */
+int64_t gdpa_launch_count(void);
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int32_t gdpa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GDPA_B200_H_ */
