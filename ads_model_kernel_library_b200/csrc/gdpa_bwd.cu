@@ -1,9 +1,522 @@
-// placeholder until the backward kernel lands
+// GDPA backward for sm_100a: dQ, dK, dV of  O = cast(act(Q K^T) * scale) V  over a jagged batch,
+// with S and P recomputed (nothing but Q, K, V, dO is read).
+//
+// One persistent CTA per SM walks a longest-first list of work items (sequence, head, 128-row KV
+// tile).  The item's K and V tiles stay resident in shared memory; Q and dO tiles of the sequence
+// stream through two-stage rings.  Per Q tile m the tensor cores run five contractions, with the KV
+// rows as the M dimension of the "transposed" score tiles:
+//
+//   S^T  = K Q_m^T          (smem x smem)        -> TMEM [0,128)
+//   dP^T = V dO_m^T         (smem x smem)        -> TMEM [128,256)
+//   dV  += P^T dO_m         (P^T bf16 in TMEM, overwriting S^T)  -> TMEM [256,256+D)
+//   dK  += dS^T Q_m         (dS^T bf16 in smem)  -> TMEM [384,384+D)
+//   dQ_m = dS K             (same smem tile read MN-major)       -> TMEM [128,128+D), aliasing dP^T
+//
+// issued in the order S(m), dQ(m-1), dK(m-1), dP(m), dV(m) so that the element-wise work of tile m
+// (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
+// dQ tiles are drained by a dedicated warpgroup and added into an fp32 accumulator with vector
+// reductions; a second kernel rounds the accumulator to bf16.
+//
+// Roles (16 warps): warps 0-3 dQ reduce, warps 4-11 element-wise (warp w: TMEM lanes 32*(w%4),
+// score columns 64*((w-4)/4)), warp 12 MMA issuer, warp 13 TMA loader, warps 14-15 idle.
+//
+// Masking is by zero: score entries whose KV row or Q column lies beyond the sequence are zeroed
+// both in act(S) and in act'(S) (act'(0) is not 0 for GELU / SiLU), so rows of other sequences that
+// a tile overlaps contribute exactly zero.
 #include "gdpa_common.cuh"
 #include "gdpa_launch.h"
+
 namespace gdpa {
-int launch_bwd_bf16(const BwdLaunch&, int, int) { return GDPA_ERR_UNSUPPORTED_ACT_; }
-int launch_dq_convert(const float*, __nv_bfloat16*, long long, cudaStream_t) { return GDPA_ERR_UNSUPPORTED_ACT_; }
+
+namespace {
+
+constexpr int kBwdThreads = 16 * 32;
+constexpr int kBwdMmaWarp = 12;
+constexpr int kBwdLoadWarp = 13;
+constexpr int kRegsCompute = 168;
+constexpr int kRegsReduce = 80;
+constexpr int kRegsOther = 80;
+
+enum BwdBar : int {
+  BB_KV_FULL = 0,
+  BB_KV_EMPTY = 1,
+  BB_Q_FULL = 2,    // [2]
+  BB_Q_EMPTY = 4,   // [2]
+  BB_DO_FULL = 6,   // [2]
+  BB_DO_EMPTY = 8,  // [2]
+  BB_S_FULL = 10,
+  BB_P_FULL = 11,   // 256 arrivals
+  BB_DP_FULL = 12,
+  BB_DS_FULL = 13,  // 256 arrivals
+  BB_DQ_FULL = 14,
+  BB_DQ_EMPTY = 15, // 128 arrivals
+  BB_DKV_FULL = 16,
+  BB_DKV_EMPTY = 17,// 256 arrivals
+  BB_COUNT = 18
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kHalfBytes = kTile * 64 * 2;
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kTileBytes;
+  static constexpr int kQOff = 2 * kTileBytes;            // 2 stages
+  static constexpr int kDoOff = 4 * kTileBytes;           // 2 stages
+  static constexpr int kDsOff = 6 * kTileBytes;           // 128 x 128 bf16, two swizzled boxes
+  static constexpr int kDsBytes = kTile * kTile * 2;
+  static constexpr int kBarOff = kDsOff + kDsBytes;
+  static constexpr int kTmemPtrOff = kBarOff + BB_COUNT * 8;
+  static constexpr int kAbortOff = kTmemPtrOff + 4;
+  static constexpr int kBytes = kAbortOff + 4;
+  static constexpr int kDynBytes = kBytes + 1024;
+};
+
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+#define GDPA_WAIT(bar_idx, parity, role)                                                                   \
+  if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
+    goto role_done;
+
+template <int D, int ACT>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const BwdArgs a) {
+  using L = BwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::kBarOff;
+  volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < BB_COUNT; ++i) {
+      uint32_t cnt = 1;
+      if (i == BB_P_FULL || i == BB_DS_FULL || i == BB_DKV_EMPTY) cnt = 256;
+      if (i == BB_DQ_EMPTY) cnt = 128;
+      mbar_init(bar_base + 8u * i, cnt);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kBwdMmaWarp) {
+    tmem_alloc(smem_base + L::kTmemPtrOff, 512);
+    tmem_relinquish();
+  }
+  if (warp == kBwdLoadWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_do);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+  const int n_items = a.sched[0];
+
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
+  // S^T / dP^T: A and B both K-major (head dim contiguous), M = N = 128.
+  constexpr uint32_t kIdescKK = umma_idesc(1, 1, 0, 0, kTile, kTile);
+  // dV, dK: A K-major (TMEM or smem), B MN-major (dO / Q rows hold the head dim), N = D.
+  constexpr uint32_t kIdescKM = umma_idesc(1, 1, 0, 1, kTile, D);
+  // dQ: A = dS read MN-major (Q index contiguous in smem), B = K tile MN-major, N = D.
+  constexpr uint32_t kIdescMM = umma_idesc(1, 1, 1, 1, kTile, D);
+
+  if (warp >= 12) {
+    reg_dec<kRegsOther>();
+    if (warp == kBwdLoadWarp) {
+      // ---------------------------------------------------------------- TMA loader
+      if (lane == 0) {
+        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase[2] = {0, 0}, st = 0;
+        WorkWalker walker(n_items);
+        int idx;
+        while (walker.next(idx)) {
+          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+          const int nq = (w.lq + kTile - 1) / kTile;
+          if (nq == 0) continue;
+          const int kv_row = static_cast<int>(w.kv_start) + w.blk * kTile;
+          const int q_row = static_cast<int>(w.q_start);
+          GDPA_WAIT(BB_KV_EMPTY, kv_phase ^ 1u, ST_ROLE_LOAD);
+          kv_phase ^= 1u;
+          {
+            const uint32_t bar = bar_base + 8u * BB_KV_FULL;
+            mbar_arrive_expect_tx(bar, 2 * L::kTileBytes);
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf)
+              tma_load_3d(smem_base + L::kKOff + hf * L::kHalfBytes, &tm_k, bar, hf * 64, w.h, kv_row);
+#pragma unroll
+            for (int hf = 0; hf < D / 64; ++hf)
+              tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v, bar, hf * 64, w.h, kv_row);
+          }
+          for (int m = 0; m < nq; ++m) {
+            GDPA_WAIT(BB_Q_EMPTY + st, q_phase[st] ^ 1u, ST_ROLE_LOAD);
+            q_phase[st] ^= 1u;
+            {
+              const uint32_t bar = bar_base + 8u * (BB_Q_FULL + st);
+              mbar_arrive_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, w.h,
+                            q_row + m * kTile);
+            }
+            GDPA_WAIT(BB_DO_EMPTY + st, do_phase[st] ^ 1u, ST_ROLE_LOAD);
+            do_phase[st] ^= 1u;
+            {
+              const uint32_t bar = bar_base + 8u * (BB_DO_FULL + st);
+              mbar_arrive_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kDoOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_do, bar, hf * 64,
+                            w.h, q_row + m * kTile);
+            }
+            st ^= 1u;
+          }
+        }
+      }
+    } else if (warp == kBwdMmaWarp) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase[2] = {0, 0}, st = 0;
+        uint32_t p_phase = 0, ds_phase = 0, dqe_phase = 0, dkve_phase = 0;
+        const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff, sDs = smem_base + L::kDsOff;
+        // A, B K-major over the head dim: D / 16 slices.
+        auto mma_kmajor_pair = [&](uint32_t d_col, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+            umma_ss_f16(tmem_base + d_col, umma_smem_desc_sw128(a_base + off, 16, 1024),
+                        umma_smem_desc_sw128(b_base + off, 16, 1024), kIdescKK, kk > 0 ? 1u : 0u);
+          }
+        };
+        WorkWalker walker(n_items);
+        int idx;
+        while (walker.next(idx)) {
+          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+          const int nq = (w.lq + kTile - 1) / kTile;
+          if (nq == 0) continue;
+          GDPA_WAIT(BB_KV_FULL, kv_phase, ST_ROLE_MMA);
+          kv_phase ^= 1u;
+          for (int m = 0; m <= nq; ++m) {
+            const uint32_t sQ = smem_base + L::kQOff + st * L::kTileBytes;
+            const uint32_t sDo = smem_base + L::kDoOff + st * L::kTileBytes;
+            if (m < nq) {
+              GDPA_WAIT(BB_Q_FULL + st, q_phase[st], ST_ROLE_MMA);
+              q_phase[st] ^= 1u;
+              tc_fence_after();
+              mma_kmajor_pair(kColS, sK, sQ);  // S^T = K Q_m^T
+              tc_commit(bar_base + 8u * BB_S_FULL);
+            }
+            if (m > 0) {
+              const uint32_t pst = st ^ 1u;
+              const uint32_t sQp = smem_base + L::kQOff + pst * L::kTileBytes;
+              GDPA_WAIT(BB_DS_FULL, ds_phase, ST_ROLE_MMA);
+              ds_phase ^= 1u;
+              tc_fence_after();
+              // dQ_{m-1} = dS K : A = dS^T tile read MN-major, B = K tile MN-major, 8 slices of 16 KV rows
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                umma_ss_f16(tmem_base + kColDP, umma_smem_desc_sw128(sDs + kk * 2048, L::kHalfBytes, 1024),
+                            umma_smem_desc_sw128(sK + kk * 2048, L::kHalfBytes, 1024), kIdescMM, kk > 0 ? 1u : 0u);
+              tc_commit(bar_base + 8u * BB_DQ_FULL);
+              // dK += dS^T Q_{m-1} : A = dS^T K-major over q, B = Q tile MN-major
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk) {
+                const uint32_t aoff = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+                umma_ss_f16(tmem_base + kColDK, umma_smem_desc_sw128(sDs + aoff, 16, 1024),
+                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            (m > 1 || kk > 0) ? 1u : 0u);
+              }
+              tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
+            }
+            if (m < nq) {
+              GDPA_WAIT(BB_DO_FULL + st, do_phase[st], ST_ROLE_MMA);
+              do_phase[st] ^= 1u;
+              GDPA_WAIT(BB_DQ_EMPTY, dqe_phase ^ 1u, ST_ROLE_MMA);
+              dqe_phase ^= 1u;
+              tc_fence_after();
+              mma_kmajor_pair(kColDP, sV, sDo);  // dP^T = V dO_m^T
+              tc_commit(bar_base + 8u * BB_DP_FULL);
+              GDPA_WAIT(BB_P_FULL, p_phase, ST_ROLE_MMA);
+              p_phase ^= 1u;
+              if (m == 0) {
+                GDPA_WAIT(BB_DKV_EMPTY, dkve_phase ^ 1u, ST_ROLE_MMA);
+                dkve_phase ^= 1u;
+              }
+              tc_fence_after();
+              // dV += P^T dO_m : A = P^T (bf16 in TMEM over the S^T columns), B = dO tile MN-major
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                umma_ts_f16(tmem_base + kColDV, tmem_base + kColS + kk * 8,
+                            umma_smem_desc_sw128(sDo + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            (m > 0 || kk > 0) ? 1u : 0u);
+              tc_commit(bar_base + 8u * (BB_DO_EMPTY + st));
+              st ^= 1u;
+            }
+          }
+          tc_commit(bar_base + 8u * BB_DKV_FULL);
+          tc_commit(bar_base + 8u * BB_KV_EMPTY);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ element-wise warps
+    reg_inc<kRegsCompute>();
+    const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;
+    const int row = quarter * 32 + lane;  // KV row of the tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + kColS, tDP = tmem_base + lane_base + kColDP;
+    const float scale = a.scale, hscale = 0.5f * a.scale;
+    uint8_t* sds_row = smem + L::kDsOff + half * L::kHalfBytes + row * 128;
+    uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0;
+    WorkWalker walker(n_items);
+    int idx;
+    while (walker.next(idx)) {
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const int nq = (w.lq + kTile - 1) / kTile;
+      const int kv_local = w.blk * kTile + row;
+      const bool row_valid = kv_local < w.lkv;
+      __nv_bfloat16* dk_row = a.dk + ((w.kv_start + kv_local) * a.heads + w.h) * static_cast<long long>(D);
+      __nv_bfloat16* dv_row = a.dv + ((w.kv_start + kv_local) * a.heads + w.h) * static_cast<long long>(D);
+      if (nq == 0) {
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i) {
+            reinterpret_cast<uint4*>(dk_row)[half * (D / 16) + i] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(dv_row)[half * (D / 16) + i] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      const bool tile_rows_full = (w.blk + 1) * kTile <= w.lkv;
+      for (int m = 0; m < nq; ++m) {
+        const int qv = min(kTile, w.lq - m * kTile);  // valid Q columns of this tile
+        const bool full = tile_rows_full && qv == kTile;
+        float g[64];
+        uint32_t pk[32];
+        GDPA_WAIT(BB_S_FULL, s_phase, ST_ROLE_ACT);
+        s_phase ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tS + half * 64 + c * 32, r);
+          tmem_wait_ld();
+          if (full) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float p0, p1;
+              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale, p0, g[c * 32 + 2 * i]);
+              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale, p1, g[c * 32 + 2 * i + 1]);
+              pk[c * 16 + i] = pack_bf16x2(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = half * 64 + c * 32 + 2 * i;
+              float p0, p1, g0, g1;
+              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale, p0, g0);
+              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale, p1, g1);
+              const bool v0 = row_valid && (col < qv), v1 = row_valid && (col + 1 < qv);
+              g[c * 32 + 2 * i] = v0 ? g0 : 0.f;
+              g[c * 32 + 2 * i + 1] = v1 ? g1 : 0.f;
+              pk[c * 16 + i] = pack_bf16x2(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+            }
+          }
+        }
+        // Both column halves must have read S^T before either overwrites it with P^T.
+        named_bar_sync(1, 256);
+        {
+          uint32_t lo[16], hi[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            lo[i] = pk[i];
+            hi[i] = pk[16 + i];
+          }
+          tmem_st16(tS + half * 32, lo);
+          tmem_st16(tS + half * 32 + 16, hi);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_base + 8u * BB_P_FULL);
+
+        GDPA_WAIT(BB_DP_FULL, dp_phase, ST_ROLE_ACT);
+        dp_phase ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tDP + half * 64 + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(g[c * 32 + 8 * j + 0] * __uint_as_float(r[8 * j + 0]), g[c * 32 + 8 * j + 1] * __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(g[c * 32 + 8 * j + 2] * __uint_as_float(r[8 * j + 2]), g[c * 32 + 8 * j + 3] * __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(g[c * 32 + 8 * j + 4] * __uint_as_float(r[8 * j + 4]), g[c * 32 + 8 * j + 5] * __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(g[c * 32 + 8 * j + 6] * __uint_as_float(r[8 * j + 6]), g[c * 32 + 8 * j + 7] * __uint_as_float(r[8 * j + 7]));
+            // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
+            *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_base + 8u * BB_DS_FULL);
+      }
+      // dK / dV of this KV tile: TMEM -> bf16 -> global, rows inside the sequence only.
+      GDPA_WAIT(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
+      dkv_phase ^= 1u;
+      tc_fence_after();
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const uint32_t tcol = tmem_base + lane_base + (t == 0 ? kColDV : kColDK) + half * (D / 2);
+        __nv_bfloat16* dst_row = (t == 0 ? dv_row : dk_row) + half * (D / 2);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tcol + c * 32, r);
+          tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              reinterpret_cast<uint4*>(dst_row + c * 32)[j] = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_base + 8u * BB_DKV_EMPTY);
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ reduce warps 0-3
+    reg_dec<kRegsReduce>();
+    const int row = warp * 32 + lane;  // Q row of the tile == TMEM lane
+    const uint32_t tDQ = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColDP;
+    uint32_t dq_phase = 0;
+    WorkWalker walker(n_items);
+    int idx;
+    while (walker.next(idx)) {
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const int nq = (w.lq + kTile - 1) / kTile;
+      for (int m = 0; m < nq; ++m) {
+        const int q_local = m * kTile + row;
+        const bool valid = q_local < w.lq;
+        float* dst = a.dq_accum + ((w.q_start + q_local) * a.heads + w.h) * static_cast<long long>(D);
+        GDPA_WAIT(BB_DQ_FULL, dq_phase, ST_ROLE_RED);
+        dq_phase ^= 1u;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tDQ + c * 32, r);
+          tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
+          }
+          if (valid) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          }
+        }
+      }
+    }
+  }
+
+role_done:
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+#undef GDPA_WAIT
+
+__global__ void __launch_bounds__(256) gdpa_dq_convert_kernel(const float4* __restrict__ acc, uint2* __restrict__ dq,
+                                                              long long n4) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = acc[i];
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    dq[i] = o;
+  }
+}
+
+template <int D, int ACT>
+int launch_bwd_inst(const BwdLaunch& l) {
+  using L = BwdSmem<D>;
+  auto kernel = gdpa_bwd_kernel<D, ACT>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
+  if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
+  kernel<<<l.grid, kBwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.args);
+  return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
+}
+
+template <int D>
+int launch_bwd_d(const BwdLaunch& l, int act_class) {
+  switch (act_class) {
+    case ACT_RAW: return launch_bwd_inst<D, ACT_RAW>(l);
+    case ACT_GELU_ERF: return launch_bwd_inst<D, ACT_GELU_ERF>(l);
+    case ACT_GELU_TANH: return launch_bwd_inst<D, ACT_GELU_TANH>(l);
+    case ACT_LEAKY_RELU: return launch_bwd_inst<D, ACT_LEAKY_RELU>(l);
+    case ACT_RELU: return launch_bwd_inst<D, ACT_RELU>(l);
+    case ACT_SILU: return launch_bwd_inst<D, ACT_SILU>(l);
+    case ACT_HARDSWISH: return launch_bwd_inst<D, ACT_HARDSWISH>(l);
+    case ACT_RELU_SQUARE: return launch_bwd_inst<D, ACT_RELU_SQUARE>(l);
+    default: return GDPA_ERR_UNSUPPORTED_ACT_;
+  }
+}
+
+}  // namespace
+
+int launch_bwd_bf16(const BwdLaunch& l, int head_dim, int act_class) {
+  if (head_dim == 128) return launch_bwd_d<128>(l, act_class);
+  if (head_dim == 64) return launch_bwd_d<64>(l, act_class);
+  return GDPA_ERR_UNSUPPORTED_DIM_;
+}
+
+int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {
+  const long long n4 = n / 4;  // heads * head_dim is a multiple of 64
+  if (n4 == 0) return 0;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  gdpa_dq_convert_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(reinterpret_cast<const float4*>(acc),
+                                                                      reinterpret_cast<uint2*>(dq), n4);
+  return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
+}
+
+// Softmax and FP8 forward live in their own translation units once built.
 int launch_fwd_softmax_bf16(const FwdLaunch&, int) { return GDPA_ERR_UNSUPPORTED_ACT_; }
 int launch_fwd_fp8(const FwdLaunch&, int, int) { return GDPA_ERR_UNSUPPORTED_ACT_; }
-}
+
+}  // namespace gdpa
