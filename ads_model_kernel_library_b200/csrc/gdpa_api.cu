@@ -194,6 +194,7 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.kv_blk_off = p->kv_block_offsets;
   l.grid = di.sm_count;
   l.stream = static_cast<cudaStream_t>(stream);
+  if (p->timing_start_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_start_event), l.stream);
   if (fp8) {
     rc = launch_fwd_fp8(l, p->head_dim, act);
   } else if (act == ACT_SOFTMAX) {
@@ -201,6 +202,7 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   } else {
     rc = launch_fwd_bf16(l, p->head_dim, act);
   }
+  if (p->timing_stop_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_stop_event), l.stream);
   if (rc == 0) g_launches.fetch_add(1);
   return rc;
 }
@@ -265,7 +267,9 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+  if (p->timing_start_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_start_event), st);
   rc = launch_bwd_bf16(l, p->head_dim, act);
+  if (p->timing_stop_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_stop_event), st);
   if (rc != 0) return rc;
   rc = launch_dq_convert(static_cast<const float*>(p->dq_accum), static_cast<__nv_bfloat16*>(p->dq),
                          static_cast<long long>(elems_q), st);

@@ -5,6 +5,7 @@ from .ops import (  # noqa: F401
     generalized_dot_product_attention,
     generalized_dot_product_attention_fp8,
     kernel_status,
+    kernel_timing,
     quantize_fp8_blockwise,
 )
 from .sharding import plan_token_balanced_shards, shard_jagged  # noqa: F401

@@ -76,6 +76,8 @@ class GdpaFwdParams(C.Structure):
         ("v_scales", C.c_void_p),
         ("q_block_offsets", C.c_void_p),
         ("kv_block_offsets", C.c_void_p),
+        ("timing_start_event", C.c_void_p),
+        ("timing_stop_event", C.c_void_p),
     ]
 
 
@@ -105,6 +107,8 @@ class GdpaBwdParams(C.Structure):
         ("schedule", C.c_void_p),
         ("dq_accum", C.c_void_p),
         ("status", C.c_void_p),
+        ("timing_start_event", C.c_void_p),
+        ("timing_stop_event", C.c_void_p),
     ]
 
 

@@ -19,6 +19,37 @@ from .math import SOFTMAX_ID, activation_string_to_int
 
 _SUPPORTED_HEAD_DIMS = (64, 128)
 _status_words = {}
+_timing_events = {"fwd": None, "bwd": None}
+
+
+class kernel_timing:
+    """Context manager for benchmarks: record a pair of ``torch.cuda.Event`` (``enable_timing=True``)
+    immediately around the main forward and/or backward kernel of every operator call made inside
+    the block, so that the kernel can be timed without the schedule build, the accumulator memset
+    and the dQ rounding pass."""
+
+    def __init__(self, fwd=None, bwd=None):
+        self.new = {"fwd": fwd, "bwd": bwd}
+
+    def __enter__(self):
+        self.old = dict(_timing_events)
+        for pair in self.new.values():
+            if pair is not None:
+                for ev in pair:  # events are created lazily by their first record
+                    ev.record()
+        _timing_events.update(self.new)
+        return self
+
+    def __exit__(self, *exc):
+        _timing_events.update(self.old)
+        return False
+
+
+def _set_timing(p, which: str) -> None:
+    pair = _timing_events[which]
+    if pair is not None:
+        p.timing_start_event = pair[0].cuda_event
+        p.timing_stop_event = pair[1].cuda_event
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -135,6 +166,7 @@ def _gdpa_forward_op(
                                 max_seq_len_q, max_seq_len_kv)
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
+        _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
     return o
 
@@ -189,6 +221,7 @@ def _gdpa_backward_op(
         p.schedule = sched.data_ptr()
         p.dq_accum = dq_accum.data_ptr()
         p.status = _status_word(query.device).data_ptr()
+        _set_timing(p, "bwd")
         _cabi.check(_cabi.lib.gdpa_bwd(C.byref(p), _stream_ptr()), "gdpa_bwd")
     return dq, dk, dv
 
@@ -249,6 +282,7 @@ def _gdpa_forward_fp8_op(
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_FP8_E4M3)
         p.q_scales, p.k_scales, p.v_scales = q_scales.data_ptr(), k_scales.data_ptr(), v_scales.data_ptr()
         p.q_block_offsets, p.kv_block_offsets = q_block_offsets.data_ptr(), kv_block_offsets.data_ptr()
+        _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd_fp8(C.byref(p), _stream_ptr()), "gdpa_fwd_fp8")
     return o
 

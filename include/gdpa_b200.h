@@ -142,6 +142,10 @@ typedef struct GdpaFwdParams {
   const float* v_scales;
   const void* q_block_offsets;  /* [batch + 1], same integer type as the offsets */
   const void* kv_block_offsets; /* [batch + 1] */
+  /* Optional cudaEvent_t pair recorded on `stream` immediately before and after the main kernel
+   * launch, so that a benchmark can time that kernel alone.  Null = not recorded. */
+  void* timing_start_event;
+  void* timing_stop_event;
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
@@ -183,6 +187,10 @@ typedef struct GdpaBwdParams {
   const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_BWD) */
   void* dq_accum;             /* scratch: gdpa_bwd_workspace_bytes() bytes; zeroed by gdpa_bwd */
   int32_t* status;
+  /* Optional cudaEvent_t pair recorded around the main backward kernel only (not around the
+   * accumulator memset and the fp32 -> bf16 dQ rounding kernel).  Null = not recorded. */
+  void* timing_start_event;
+  void* timing_stop_event;
 } GdpaBwdParams;
 
 /* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */

@@ -1,0 +1,174 @@
+"""GPU parity tests: the CUDA kernels (through the torch op, which calls the C ABI) against the CPU
+oracle on the same seeded inputs.  bf16 kernels vs the fp32 oracle evaluated on the bf16-rounded
+inputs: atol = rtol = 2e-2 on O, dQ, dK, dV."""
+import numpy as np
+import pytest
+import torch
+
+from tests._util import ATOL, RTOL, assert_close, jagged_inputs, oracle_forward, oracle_forward_backward
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    import ads_model_kernel_library_b200.gdpa as g
+
+    return g
+
+
+def run_fwd(G, dev, lq, lk, act, scale, max_q=None, max_kv=None):
+    o = G.generalized_dot_product_attention(
+        dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"],
+        int(max(lq)) if max_q is None else max_q, int(max(lk)) if max_kv is None else max_kv,
+        qk_scale=scale, activation=act)
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    return o
+
+
+def run_fwd_bwd(G, dev, lq, lk, act, scale):
+    q, k, v = (dev[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+    o = G.generalized_dot_product_attention(q, k, v, dev["qo"], dev["ko"], int(max(lq)), int(max(lk)),
+                                            qk_scale=scale, activation=act)
+    o.backward(dev["do"])
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    return o, q.grad, k.grad, v.grad
+
+
+ALL_ACTS = ["raw", "gelu", "gelu_approx", "fast_gelu", "leaky_relu", "relu", "fast_gelu_bf16", "silu", "fast_silu",
+            "hardswish", "relu_square", "fast_gelu_taylor_approx"]
+
+
+@pytest.mark.parametrize("act", ALL_ACTS)
+@pytest.mark.parametrize("D", [64, 128])
+def test_forward_backward_every_activation(G, act, D):
+    lq, lk = [70, 300, 129], [200, 131, 260]
+    # std 0.5 keeps |O| of order one for every activation (relu_square grows like S^2), which is the
+    # range the absolute tolerance is meant for
+    cpu, dev = jagged_inputs(lq, lk, 2, D, seed=3, std=0.5)
+    scale = 1.0 / 64
+    o, dq, dk, dv = run_fwd_bwd(G, dev, lq, lk, act, scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, act, scale)
+    assert_close(o, ro, f"O[{act}]")
+    assert_close(dq, rdq, f"dQ[{act}]")
+    assert_close(dk, rdk, f"dK[{act}]")
+    assert_close(dv, rdv, f"dV[{act}]")
+
+
+EDGE_LENS = [1, 2, 15, 16, 17, 127, 128, 129, 255, 256, 257, 383, 385, 512, 513]
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_edge_lengths_q_and_kv_differ(G, D):
+    lq = EDGE_LENS
+    lk = list(reversed(EDGE_LENS))
+    cpu, dev = jagged_inputs(lq, lk, 3, D, seed=11, std=0.5)
+    scale = 1.0 / 32
+    o, dq, dk, dv = run_fwd_bwd(G, dev, lq, lk, "gelu_approx", scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "gelu_approx", scale)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+
+
+def test_empty_sequences_and_single_sequence(G):
+    # sequences with no queries, with no keys, with neither
+    lq, lk = [0, 5, 130, 0, 64], [7, 0, 140, 0, 64]
+    cpu, dev = jagged_inputs(lq, lk, 2, 128, seed=5)
+    o, dq, dk, dv = run_fwd_bwd(G, dev, lq, lk, "silu", 0.05)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "silu", 0.05)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+    # B = 1
+    cpu, dev = jagged_inputs([200], [300], 1, 64, seed=6)
+    o, dq, dk, dv = run_fwd_bwd(G, dev, [200], [300], "relu", 0.1)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "relu", 0.1)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+
+
+def test_int32_offsets_and_default_scale(G):
+    lq, lk = [33, 257], [129, 64]
+    cpu, dev = jagged_inputs(lq, lk, 2, 128, seed=8, std=0.3, offset_dtype=torch.int32)
+    o = G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 257, 129,
+                                            activation="gelu_approx")  # qk_scale=None -> 1.0
+    ro = oracle_forward(cpu, "gelu_approx", None)
+    assert_close(o, ro, "O")
+
+
+def test_max_seq_len_clamps_lengths_like_the_reference(G):
+    # The reference clamps each sequence to max_seq_len (qlen = min(qlen, N_CTX)); rows beyond are not written.
+    lq, lk = [300, 100], [400, 90]
+    cpu, dev = jagged_inputs(lq, lk, 1, 128, seed=9)
+    o = run_fwd(G, dev, lq, lk, "relu", 0.1, max_q=200, max_kv=256)
+    cpu2 = dict(cpu)
+    # oracle on the clamped geometry
+    from oracle import gdpa_oracle as orc
+    q, k, v = cpu["q"].float(), cpu["k"].float(), cpu["v"].float()
+    exp0 = orc.gdpa_forward(q[:200], k[:256], v[:256], torch.tensor([0, 200]), torch.tensor([0, 256]), "relu", 0.1)
+    exp1 = orc.gdpa_forward(q[300:400], k[400:490], v[400:490], torch.tensor([0, 100]), torch.tensor([0, 90]), "relu", 0.1)
+    assert_close(o[:200], exp0, "O[seq0 clamped]")
+    assert_close(o[300:400], exp1, "O[seq1]")
+
+
+def test_forward_is_bitwise_deterministic_and_backward_repeatable(G):
+    lq, lk = [500, 77, 1000], [640, 300, 900]
+    cpu, dev = jagged_inputs(lq, lk, 4, 128, seed=12, std=0.5)
+    o1, dq1, dk1, dv1 = run_fwd_bwd(G, dev, lq, lk, "gelu_approx", 1e-3)
+    o2, dq2, dk2, dv2 = run_fwd_bwd(G, dev, lq, lk, "gelu_approx", 1e-3)
+    assert torch.equal(o1, o2)
+    assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
+    assert_close(dq1, dq2.float(), "dQ repeat", atol=1e-2, rtol=1e-2)  # fp32 reductions may reorder
+
+
+def test_config1_shapes_fwd_bwd(G):
+    """The reference's CPU-runnable configuration: B=8, H=2, D=64, lengths U[16,256], GELU-tanh,
+    scale 1/max_kv, N(0,1) inputs."""
+    from ads_model_kernel_library_b200.gdpa.workloads import make_workload
+
+    w = make_workload("c1_cpu_small")
+    cpu, dev = jagged_inputs(w.q_lens, w.kv_lens, w.heads, w.head_dim, seed=0)
+    o, dq, dk, dv = run_fwd_bwd(G, dev, w.q_lens, w.kv_lens, w.activation, w.qk_scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, w.activation, w.qk_scale)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+
+
+def test_reduced_config3_and_linearity_in_v_at_scale(G):
+    """Self-attention lengths U[512,4096], H=8, D=128, N(0,0.5): a few sequences against the oracle,
+    and a size-independent property on a larger batch: O is linear in V, so
+    O(V1 + V2) == O(V1) + O(V2) up to bf16 rounding."""
+    rng = np.random.default_rng(2)
+    ln = rng.integers(512, 4097, 3)
+    cpu, dev = jagged_inputs(ln, ln, 8, 128, seed=2, std=0.5)
+    scale = 1.0 / int(ln.max())
+    o, dq, dk, dv = run_fwd_bwd(G, dev, ln, ln, "gelu_approx", scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "gelu_approx", scale)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+    ln = rng.integers(512, 4097, 64)
+    _, dev = jagged_inputs(ln, ln, 8, 128, seed=3, std=0.5)
+    v2 = torch.randn_like(dev["v"]) * 0.5
+    f = lambda v: G.generalized_dot_product_attention(dev["q"], dev["k"], v, dev["qo"], dev["ko"], int(ln.max()),
+                                                      int(ln.max()), qk_scale=scale, activation="gelu_approx").float()
+    lhs = f((dev["v"].float() + v2.float()).to(torch.bfloat16))
+    rhs = f(dev["v"]) + f(v2)
+    assert G.kernel_status() == 0
+    assert_close(lhs, rhs, "linearity in V", atol=ATOL, rtol=RTOL)
+
+
+def test_host_errors_are_raised_before_any_launch(G):
+    cpu, dev = jagged_inputs([10], [12], 1, 64, seed=1)
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 10, 12, activation="tanh")
+    with pytest.raises(NotImplementedError):
+        G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 10, 12, is_causal=True)
+    with pytest.raises(TypeError):
+        G.generalized_dot_product_attention(dev["q"].float(), dev["k"].float(), dev["v"].float(), dev["qo"], dev["ko"], 10, 12)
+    q96 = torch.zeros(10, 1, 96, dtype=torch.bfloat16, device="cuda")
+    k96 = torch.zeros(12, 1, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        G.generalized_dot_product_attention(q96, k96, k96, dev["qo"], dev["ko"], 10, 12)
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"][:1], 10, 12)
