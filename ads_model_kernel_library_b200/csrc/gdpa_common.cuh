@@ -115,6 +115,36 @@ __device__ __forceinline__ float act_scaled(float x, float scale, float hscale) 
   }
 }
 
+// Two activations at once, packed bf16x2 result (x0 in the low half).  GELU-tanh and SiLU use packed
+// f32x2 arithmetic around the two MUFU evaluations; the other classes fall back to the scalar form.
+template <int ACT>
+__device__ __forceinline__ uint32_t act_scaled_pair_bf16(float x0, float x1, float scale, float hscale) {
+  if constexpr (ACT == ACT_GELU_TANH) {
+    const uint64_t X = pack_f32x2(x0, x1);
+    const uint64_t X2 = mul_f32x2(X, X);
+    const uint64_t INNER = fma_f32x2(X2, pack_f32x2(0.7978845608028654f * 0.044715f, 0.7978845608028654f * 0.044715f),
+                                     pack_f32x2(0.7978845608028654f, 0.7978845608028654f));
+    float u0, u1;
+    unpack_f32x2(mul_f32x2(X, INNER), u0, u1);
+    const uint64_t T = pack_f32x2(tanh_approx(u0), tanh_approx(u1));
+    const uint64_t XS = mul_f32x2(X, pack_f32x2(hscale, hscale));
+    float p0, p1;
+    unpack_f32x2(fma_f32x2(XS, T, XS), p0, p1);
+    return pack_bf16x2(p0, p1);
+  } else if constexpr (ACT == ACT_SILU) {
+    const uint64_t X = pack_f32x2(x0, x1);
+    float h0, h1;
+    unpack_f32x2(mul_f32x2(X, pack_f32x2(0.5f, 0.5f)), h0, h1);
+    const uint64_t T = pack_f32x2(tanh_approx(h0), tanh_approx(h1));
+    const uint64_t XS = mul_f32x2(X, pack_f32x2(hscale, hscale));
+    float p0, p1;
+    unpack_f32x2(fma_f32x2(XS, T, XS), p0, p1);
+    return pack_bf16x2(p0, p1);
+  } else {
+    return pack_bf16x2(act_scaled<ACT>(x0, scale, hscale), act_scaled<ACT>(x1, scale, hscale));
+  }
+}
+
 // act(x) and act'(x), both already multiplied by `scale`.
 template <int ACT>
 __device__ __forceinline__ void act_and_grad_scaled(float x, float scale, float hscale, float& p, float& g) {

@@ -2,14 +2,15 @@
 //
 // One persistent CTA per SM walks a longest-first list of work items (sequence, head, 256-row
 // Q block).  A work item keeps two 128-row Q tiles resident in shared memory and streams the
-// sequence's K and V tiles through a shared-memory ring.  Roles (14 warps):
+// sequence's K and V tiles through a shared-memory ring.  Roles (16 warps, registers re-divided
+// with setmaxnreg):
 //
 //   warps 0-3   activation group 0: S0 (TMEM) -> registers -> act * scale -> bf16 P0 (TMEM)
 //   warps 4-7   activation group 1: same for S1
 //   warps 8-11  epilogue: O0 / O1 (TMEM) -> registers -> bf16 -> global
 //   warp  12    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
 //               O_s += P_s V (A operand P read from TMEM)
-//   warp  13    TMA loader (one lane)
+//   warp  13    TMA loader (one lane);  warps 14-15 idle (they complete the fourth warpgroup)
 //
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).  P_s (bf16, two
 // values per column) overwrites the first 64 columns of S_s once those have been read.
@@ -27,7 +28,10 @@ namespace gdpa {
 
 namespace {
 
-constexpr int kFwdThreads = 14 * 32;
+constexpr int kFwdThreads = 16 * 32;
+constexpr int kFwdRegsAct = 152;
+constexpr int kFwdRegsEpi = 104;
+constexpr int kFwdRegsOther = 104;
 constexpr int kMmaWarp = 12;
 constexpr int kLoadWarp = 13;
 constexpr int kKvStages = 4;
@@ -106,7 +110,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // PV: A = P in TMEM, B = V tile (MN-major: head dim contiguous), M = 128, N = D.
   constexpr uint32_t kIdescPV = umma_idesc(1, 1, 0, 1, kTile, D);
 
-  if (warp == kLoadWarp) {
+  if (warp >= 12) {
+   setmaxnreg_dec<kFwdRegsOther>();
+   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA loader
     if (lane == 0) {
       uint32_t kv_stage = 0, kv_phase = 0, q_phase[2] = {0, 0};
@@ -152,7 +158,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-  } else if (warp == kMmaWarp) {
+   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t kv_stage = 0, kv_phase = 0;
@@ -231,8 +237,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
+   }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ activation groups
+    setmaxnreg_inc<kFwdRegsAct>();
     const int s = warp >> 2;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_base + s * kTile;
@@ -250,23 +258,27 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
+        // Four 32-column chunks; the TMEM load of chunk c+1 is in flight while chunk c is computed.
+        uint32_t ra[32], rb[32];
+        tmem_ld32(s_tmem, ra);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
           uint32_t pk[16];
-          tmem_ld32(s_tmem + c * 32, r);
           tmem_wait_ld();
+          tmem_regs_ready(cur);
+          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
           if (valid >= (c + 1) * 32) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              pk[i] = pack_bf16x2(act_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale),
-                                  act_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale));
+              pk[i] = act_scaled_pair_bf16<ACT>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(r[2 * i]) : 0.f;
-              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(r[2 * i + 1]) : 0.f;
-              pk[i] = pack_bf16x2(act_scaled<ACT>(x0, scale, hscale), act_scaled<ACT>(x1, scale, hscale));
+              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(cur[2 * i]) : 0.f;
+              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(cur[2 * i + 1]) : 0.f;
+              pk[i] = act_scaled_pair_bf16<ACT>(x0, x1, scale, hscale);
             }
           }
           tmem_st16(s_tmem + c * 16, pk);
@@ -278,6 +290,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 8-11)
+    setmaxnreg_dec<kFwdRegsEpi>();
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t o_phase[2] = {0, 0};
@@ -302,12 +315,18 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         GDPA_WAIT(B_O_FULL + s, o_phase[s], ST_ROLE_EPI);
         o_phase[s] ^= 1u;
         tc_fence_after();
+        const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
+        uint32_t ra[32], rb[32];
+        tmem_ld32(o_tmem, ra);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + lane_base + 256 + s * kTile + c * 32, r);
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
           tmem_wait_ld();
-          if (c == D / 32 - 1) {
+          tmem_regs_ready(cur);
+          if (c < D / 32 - 1) {
+            tmem_ld32(o_tmem + (c + 1) * 32, nxt);
+          } else {
             tc_fence_before();
             mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
           }
@@ -315,10 +334,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              v.x = pack_bf16x2(__uint_as_float(cur[8 * i + 0]), __uint_as_float(cur[8 * i + 1]));
+              v.y = pack_bf16x2(__uint_as_float(cur[8 * i + 2]), __uint_as_float(cur[8 * i + 3]));
+              v.z = pack_bf16x2(__uint_as_float(cur[8 * i + 4]), __uint_as_float(cur[8 * i + 5]));
+              v.w = pack_bf16x2(__uint_as_float(cur[8 * i + 6]), __uint_as_float(cur[8 * i + 7]));
               dst[c * 4 + i] = v;
             }
           }
