@@ -248,9 +248,9 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
   if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
   if ((rc = make_tmap(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
-  // fp32 dQ accumulator, reduced into by 32-column x 128-row unswizzled boxes.
+  // fp32 dQ accumulator, reduced into by 32-column x 32-row boxes (128-byte swizzled staging).
   if ((rc = make_tmap(&l.tm_dq, p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
-                      kTile, false)) != GDPA_OK)
+                      32, true)) != GDPA_OK)
     return rc;
   l.args.dk = static_cast<__nv_bfloat16*>(p->dk);
   l.args.dv = static_cast<__nv_bfloat16*>(p->dv);

@@ -14,11 +14,15 @@
 //
 // issued in the order S(m), dQ(m-1), dK(m-1), dP(m), dV(m) so that the element-wise work of tile m
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
-// dQ tiles are drained by a dedicated warpgroup and added into an fp32 accumulator with vector
-// reductions; a second kernel rounds the accumulator to bf16.
+// dQ tiles are drained by a dedicated warpgroup into shared memory and added into an fp32
+// accumulator by TMA reduce-add (32-column slabs, two staging buffers); a second kernel rounds the
+// accumulator to bf16.  Q rows of a tile beyond the sequence carry dS = 0, so what the reduce adds to
+// the rows of the next sequence is exactly zero; rows beyond the tensor are clipped by the TMA unit.
 //
 // Roles (16 warps): warps 0-3 dQ reduce, warps 4-11 element-wise (warp w: TMEM lanes 32*(w%4),
 // score columns 64*((w-4)/4)), warp 12 MMA issuer, warp 13 TMA loader, warps 14-15 idle.
+// P^T of column half h is written over the first 32 columns of that half's own S^T columns
+// ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
 // Masking is by zero: score entries whose KV row or Q column lies beyond the sequence are zeroed
 // both in act(S) and in act'(S) (act'(0) is not 0 for GELU / SiLU), so rows of other sequences that
@@ -34,16 +38,17 @@ constexpr int kBwdThreads = 16 * 32;
 constexpr int kBwdMmaWarp = 12;
 constexpr int kBwdLoadWarp = 13;
 constexpr int kRegsCompute = 168;
-constexpr int kRegsReduce = 80;
+constexpr int kRegsReduce = 96;
 constexpr int kRegsOther = 80;
+constexpr int kDqWarpSlabBytes = 32 * 32 * 4;  // one warp's staging slab: 32 rows x 32 fp32
 
 enum BwdBar : int {
   BB_KV_FULL = 0,
   BB_KV_EMPTY = 1,
   BB_Q_FULL = 2,    // [2]
   BB_Q_EMPTY = 4,   // [2]
-  BB_DO_FULL = 6,   // [2]
-  BB_DO_EMPTY = 8,  // [2]
+  BB_DO_FULL = 6,   // one stage
+  BB_DO_EMPTY = 8,
   BB_S_FULL = 10,
   BB_P_FULL = 11,   // 256 arrivals
   BB_DP_FULL = 12,
@@ -62,28 +67,17 @@ struct BwdSmem {
   static constexpr int kKOff = 0;
   static constexpr int kVOff = kTileBytes;
   static constexpr int kQOff = 2 * kTileBytes;            // 2 stages
-  static constexpr int kDoOff = 4 * kTileBytes;           // 2 stages
-  static constexpr int kDsOff = 6 * kTileBytes;           // 128 x 128 bf16, two swizzled boxes
+  static constexpr int kDoOff = 4 * kTileBytes;           // 1 stage
+  static constexpr int kDsOff = 5 * kTileBytes;           // 128 x 128 bf16, two swizzled boxes
   static constexpr int kDsBytes = kTile * kTile * 2;
-  static constexpr int kBarOff = kDsOff + kDsBytes;
+  static constexpr int kDqOff = kDsOff + kDsBytes;        // 2 staging slabs of 128 rows x 32 fp32
+  static constexpr int kDqSlabBytes = kTile * 32 * 4;
+  static constexpr int kBarOff = kDqOff + 2 * kDqSlabBytes;
   static constexpr int kTmemPtrOff = kBarOff + BB_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kBytes = kAbortOff + 4;
   static constexpr int kDynBytes = kBytes + 1024;
 };
-
-template <int N>
-__device__ __forceinline__ void reg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
@@ -93,7 +87,7 @@ template <int D, int ACT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const BwdArgs a) {
+                const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
   using L = BwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -125,6 +119,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_dq);
   }
   tc_fence_before();
   __syncthreads();
@@ -141,11 +136,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t kIdescMM = umma_idesc(1, 1, 1, 1, kTile, D);
 
   if (warp >= 12) {
-    reg_dec<kRegsOther>();
+    setmaxnreg_dec<kRegsOther>();
     if (warp == kBwdLoadWarp) {
       // ---------------------------------------------------------------- TMA loader
       if (lane == 0) {
-        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase[2] = {0, 0}, st = 0;
+        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase = 0, st = 0;
         WorkWalker walker(n_items);
         int idx;
         while (walker.next(idx)) {
@@ -177,15 +172,14 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, w.h,
                             q_row + m * kTile);
             }
-            GDPA_WAIT(BB_DO_EMPTY + st, do_phase[st] ^ 1u, ST_ROLE_LOAD);
-            do_phase[st] ^= 1u;
+            GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
+            do_phase ^= 1u;
             {
-              const uint32_t bar = bar_base + 8u * (BB_DO_FULL + st);
+              const uint32_t bar = bar_base + 8u * BB_DO_FULL;
               mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
               for (int hf = 0; hf < D / 64; ++hf)
-                tma_load_3d(smem_base + L::kDoOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_do, bar, hf * 64,
-                            w.h, q_row + m * kTile);
+                tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do, bar, hf * 64, w.h, q_row + m * kTile);
             }
             st ^= 1u;
           }
@@ -194,7 +188,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp == kBwdMmaWarp) {
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
-        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase[2] = {0, 0}, st = 0;
+        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase = 0, st = 0;
         uint32_t p_phase = 0, ds_phase = 0, dqe_phase = 0, dkve_phase = 0;
         const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff, sDs = smem_base + L::kDsOff;
         // A, B K-major over the head dim: D / 16 slices.
@@ -216,7 +210,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           kv_phase ^= 1u;
           for (int m = 0; m <= nq; ++m) {
             const uint32_t sQ = smem_base + L::kQOff + st * L::kTileBytes;
-            const uint32_t sDo = smem_base + L::kDoOff + st * L::kTileBytes;
+            const uint32_t sDo = smem_base + L::kDoOff;
             if (m < nq) {
               GDPA_WAIT(BB_Q_FULL + st, q_phase[st], ST_ROLE_MMA);
               q_phase[st] ^= 1u;
@@ -247,8 +241,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
             }
             if (m < nq) {
-              GDPA_WAIT(BB_DO_FULL + st, do_phase[st], ST_ROLE_MMA);
-              do_phase[st] ^= 1u;
+              GDPA_WAIT(BB_DO_FULL, do_phase, ST_ROLE_MMA);
+              do_phase ^= 1u;
               GDPA_WAIT(BB_DQ_EMPTY, dqe_phase ^ 1u, ST_ROLE_MMA);
               dqe_phase ^= 1u;
               tc_fence_after();
@@ -264,10 +258,10 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               // dV += P^T dO_m : A = P^T (bf16 in TMEM over the S^T columns), B = dO tile MN-major
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
-                umma_ts_f16(tmem_base + kColDV, tmem_base + kColS + kk * 8,
+                umma_ts_f16(tmem_base + kColDV, tmem_base + kColS + (kk >> 2) * 64 + (kk & 3) * 8,
                             umma_smem_desc_sw128(sDo + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
                             (m > 0 || kk > 0) ? 1u : 0u);
-              tc_commit(bar_base + 8u * (BB_DO_EMPTY + st));
+              tc_commit(bar_base + 8u * BB_DO_EMPTY);
               st ^= 1u;
             }
           }
@@ -278,7 +272,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ element-wise warps
-    reg_inc<kRegsCompute>();
+    setmaxnreg_inc<kRegsCompute>();
     const int quarter = warp & 3;
     const int half = (warp - 4) >> 2;
     const int row = quarter * 32 + lane;  // KV row of the tile == TMEM lane
@@ -310,49 +304,34 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int m = 0; m < nq; ++m) {
         const int qv = min(kTile, w.lq - m * kTile);  // valid Q columns of this tile
         const bool full = tile_rows_full && qv == kTile;
-        float g[64];
-        uint32_t pk[32];
+        uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
+        uint32_t ra[32], rb[32];
         GDPA_WAIT(BB_S_FULL, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
+        tmem_ld32(tS + half * 64, ra);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tS + half * 64 + c * 32, r);
+          uint32_t(&cur)[32] = c ? rb : ra;
+          uint32_t pk[16];
           tmem_wait_ld();
+          tmem_regs_ready(cur);
+          if (c == 0) tmem_ld32(tS + half * 64 + 32, rb);
           if (full) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float p0, p1;
-              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale, p0, g[c * 32 + 2 * i]);
-              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale, p1, g[c * 32 + 2 * i + 1]);
-              pk[c * 16 + i] = pack_bf16x2(p0, p1);
-            }
+            for (int i = 0; i < 16; ++i)
+              act_and_grad_pair<ACT, false>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
+                                            true, true, pk[i], g2[c * 16 + i]);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int col = half * 64 + c * 32 + 2 * i;
-              float p0, p1, g0, g1;
-              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i]), scale, hscale, p0, g0);
-              act_and_grad_scaled<ACT>(__uint_as_float(r[2 * i + 1]), scale, hscale, p1, g1);
-              const bool v0 = row_valid && (col < qv), v1 = row_valid && (col + 1 < qv);
-              g[c * 32 + 2 * i] = v0 ? g0 : 0.f;
-              g[c * 32 + 2 * i + 1] = v1 ? g1 : 0.f;
-              pk[c * 16 + i] = pack_bf16x2(v0 ? p0 : 0.f, v1 ? p1 : 0.f);
+              act_and_grad_pair<ACT, true>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
+                                           row_valid && (col < qv), row_valid && (col + 1 < qv), pk[i], g2[c * 16 + i]);
             }
           }
-        }
-        // Both column halves must have read S^T before either overwrites it with P^T.
-        named_bar_sync(1, 256);
-        {
-          uint32_t lo[16], hi[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            lo[i] = pk[i];
-            hi[i] = pk[16 + i];
-          }
-          tmem_st16(tS + half * 32, lo);
-          tmem_st16(tS + half * 32 + 16, hi);
+          // P^T chunk c of this half goes over columns this half has already read
+          tmem_st16(tS + half * 64 + c * 16, pk);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -361,20 +340,26 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         GDPA_WAIT(BB_DP_FULL, dp_phase, ST_ROLE_ACT);
         dp_phase ^= 1u;
         tc_fence_after();
+        tmem_ld32(tDP + half * 64, ra);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tDP + half * 64 + c * 32, r);
+          uint32_t(&cur)[32] = c ? rb : ra;
           tmem_wait_ld();
+          tmem_regs_ready(cur);
+          if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16x2(g[c * 32 + 8 * j + 0] * __uint_as_float(r[8 * j + 0]), g[c * 32 + 8 * j + 1] * __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16x2(g[c * 32 + 8 * j + 2] * __uint_as_float(r[8 * j + 2]), g[c * 32 + 8 * j + 3] * __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16x2(g[c * 32 + 8 * j + 4] * __uint_as_float(r[8 * j + 4]), g[c * 32 + 8 * j + 5] * __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16x2(g[c * 32 + 8 * j + 6] * __uint_as_float(r[8 * j + 6]), g[c * 32 + 8 * j + 7] * __uint_as_float(r[8 * j + 7]));
+            uint32_t d[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float d0, d1;
+              unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e],
+                                     pack_f32x2(__uint_as_float(cur[8 * j + 2 * e]), __uint_as_float(cur[8 * j + 2 * e + 1]))),
+                           d0, d1);
+              d[e] = pack_bf16x2(d0, d1);
+            }
             // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
-            *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = v;
+            *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
           }
         }
         fence_proxy_async_smem();
@@ -412,37 +397,55 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ dQ reduce warps 0-3
-    reg_dec<kRegsReduce>();
-    const int row = warp * 32 + lane;  // Q row of the tile == TMEM lane
+    setmaxnreg_dec<kRegsReduce>();
+    // Each warp drains its own 32 Q rows: TMEM -> registers -> its private staging slab (32 rows x
+    // 32 fp32, 128-byte swizzled, two buffers) -> one TMA reduce-add per slab.  No cross-warp barrier.
     const uint32_t tDQ = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColDP;
-    uint32_t dq_phase = 0;
+    uint8_t* stage_row = smem + L::kDqOff + warp * (2 * kDqWarpSlabBytes) + lane * 128;
+    const uint32_t stage_base = smem_base + L::kDqOff + warp * (2 * kDqWarpSlabBytes);
+    uint32_t dq_phase = 0, slab = 0;
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
       const int nq = (w.lq + kTile - 1) / kTile;
       for (int m = 0; m < nq; ++m) {
-        const int q_local = m * kTile + row;
-        const bool valid = q_local < w.lq;
-        float* dst = a.dq_accum + ((w.q_start + q_local) * a.heads + w.h) * static_cast<long long>(D);
-        GDPA_WAIT(BB_DQ_FULL, dq_phase, ST_ROLE_RED);
+        const int q_row0 = static_cast<int>(w.q_start) + m * kTile + warp * 32;
+        uint32_t ra[32], rb[32];
+        {
+          const bool ok = mbar_wait(bar_base + 8u * BB_DQ_FULL, dq_phase, abort_flag, a.status, (BB_DQ_FULL << 8) | ST_ROLE_RED);
+          if (!__all_sync(0xffffffffu, ok)) goto role_done;  // warp-uniform decision
+        }
         dq_phase ^= 1u;
         tc_fence_after();
+        tmem_ld32(tDQ, ra);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tDQ + c * 32, r);
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
           tmem_wait_ld();
-          if (c == D / 32 - 1) {
+          tmem_regs_ready(cur);
+          if (c < D / 32 - 1) {
+            tmem_ld32(tDQ + (c + 1) * 32, nxt);
+          } else {
             tc_fence_before();
             mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
           }
-          if (valid) {
+          const uint32_t buf = slab & 1u;
+          // the reduce that read this staging buffer two slabs ago must have finished reading it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, w.h, q_row0);
+            tma_store_commit();
           }
+          ++slab;
         }
       }
     }
@@ -450,6 +453,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 role_done:
   __syncwarp();
+  if (warp < 4 && lane == 0) tma_store_wait_all<0>();  // this warp's reduce-adds have left shared memory
   tc_fence_before();
   __syncthreads();
   if (warp == kBwdMmaWarp) {
@@ -478,7 +482,7 @@ int launch_bwd_inst(const BwdLaunch& l) {
   auto kernel = gdpa_bwd_kernel<D, ACT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
-  kernel<<<l.grid, kBwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.args);
+  kernel<<<l.grid, kBwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.tm_dq, l.args);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 

@@ -192,4 +192,62 @@ __device__ __forceinline__ void act_and_grad_scaled(float x, float scale, float 
   }
 }
 
+// Two elements at once: packed bf16x2 of act * scale (x0 in the low half) and the packed fp32 pair
+// of act' * scale.  `m0` / `m1` = element is inside the sequence; masked elements give 0 and 0.
+template <int ACT, bool MASKED>
+__device__ __forceinline__ void act_and_grad_pair(float x0, float x1, float scale, float hscale, bool m0, bool m1,
+                                                  uint32_t& p_bf16x2, uint64_t& g2) {
+  float p0, p1, g0, g1;
+  if constexpr (ACT == ACT_GELU_TANH) {
+    constexpr float c0 = 0.7978845608028654f, c1 = 0.044715f;
+    const uint64_t X = pack_f32x2(x0, x1);
+    const uint64_t X2 = mul_f32x2(X, X);
+    float u0, u1;
+    unpack_f32x2(mul_f32x2(X, fma_f32x2(X2, pack_f32x2(c0 * c1, c0 * c1), pack_f32x2(c0, c0))), u0, u1);
+    const uint64_t T = pack_f32x2(tanh_approx(u0), tanh_approx(u1));
+    const uint64_t HS = pack_f32x2(hscale, hscale);
+    const uint64_t XS = mul_f32x2(X, HS);
+    const uint64_t P = fma_f32x2(XS, T, XS);
+    const uint64_t DU = fma_f32x2(X2, pack_f32x2(3.f * c0 * c1, 3.f * c0 * c1), pack_f32x2(c0, c0));
+    const uint64_t NT = mul_f32x2(T, pack_f32x2(-1.f, -1.f));
+    const uint64_t SECH2 = fma_f32x2(NT, T, pack_f32x2(1.f, 1.f));
+    const uint64_t G = fma_f32x2(mul_f32x2(XS, SECH2), DU, fma_f32x2(T, HS, HS));
+    unpack_f32x2(P, p0, p1);
+    if constexpr (!MASKED) {
+      p_bf16x2 = pack_bf16x2(p0, p1);
+      g2 = G;
+      return;
+    }
+    unpack_f32x2(G, g0, g1);
+  } else if constexpr (ACT == ACT_SILU) {
+    const uint64_t X = pack_f32x2(x0, x1);
+    float h0, h1;
+    unpack_f32x2(mul_f32x2(X, pack_f32x2(0.5f, 0.5f)), h0, h1);
+    const uint64_t T = pack_f32x2(tanh_approx(h0), tanh_approx(h1));
+    const uint64_t SG = fma_f32x2(T, pack_f32x2(0.5f, 0.5f), pack_f32x2(0.5f, 0.5f));
+    const uint64_t SGS = mul_f32x2(SG, pack_f32x2(scale, scale));
+    const uint64_t P = mul_f32x2(X, SGS);
+    const uint64_t OM = fma_f32x2(SG, pack_f32x2(-1.f, -1.f), pack_f32x2(1.f, 1.f));
+    const uint64_t G = mul_f32x2(SGS, fma_f32x2(X, OM, pack_f32x2(1.f, 1.f)));
+    unpack_f32x2(P, p0, p1);
+    if constexpr (!MASKED) {
+      p_bf16x2 = pack_bf16x2(p0, p1);
+      g2 = G;
+      return;
+    }
+    unpack_f32x2(G, g0, g1);
+  } else {
+    act_and_grad_scaled<ACT>(x0, scale, hscale, p0, g0);
+    act_and_grad_scaled<ACT>(x1, scale, hscale, p1, g1);
+  }
+  if constexpr (MASKED) {
+    p0 = m0 ? p0 : 0.f;
+    p1 = m1 ? p1 : 0.f;
+    g0 = m0 ? g0 : 0.f;
+    g1 = m1 ? g1 : 0.f;
+  }
+  p_bf16x2 = pack_bf16x2(p0, p1);
+  g2 = pack_f32x2(g0, g1);
+}
+
 }  // namespace gdpa
