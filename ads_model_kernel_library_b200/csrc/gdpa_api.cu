@@ -105,6 +105,8 @@ const char* gdpa_strerror(int code) {
     case GDPA_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
     case GDPA_ERR_CAPACITY: return "schedule buffer too small";
     case GDPA_ERR_DEVICE: return "current device is not a compute-capability 10.x GPU";
+    case GDPA_ERR_NOALLOC_TOO_LARGE:
+      return "gdpa_fwd_noalloc: heads * (total_q / 256 + batch) exceeds GDPA_NOALLOC_MAX_ITEMS (65536); use gdpa_fwd with a caller-allocated schedule";
     default: return "unknown error code";
   }
 }

@@ -24,6 +24,7 @@ EXPORTS = (
     "gdpa_build_schedule",
     "gdpa_fwd",
     "gdpa_fwd_fp8",
+    "gdpa_fwd_noalloc",
     "gdpa_bwd_workspace_bytes",
     "gdpa_bwd",
     "gdpa_strerror",
@@ -125,6 +126,8 @@ def _load() -> C.CDLL:
     lib.gdpa_build_schedule.argtypes = [C.POINTER(GdpaSchedParams), C.c_void_p]
     lib.gdpa_fwd.restype = C.c_int
     lib.gdpa_fwd.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
+    lib.gdpa_fwd_noalloc.restype = C.c_int
+    lib.gdpa_fwd_noalloc.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
     lib.gdpa_fwd_fp8.restype = C.c_int
     lib.gdpa_fwd_fp8.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
     lib.gdpa_bwd_workspace_bytes.restype = C.c_size_t

@@ -50,7 +50,8 @@ enum {
   GDPA_ERR_LAUNCH = 6,         /* cudaGetLastError() after a launch was not cudaSuccess        */
   GDPA_ERR_DRIVER = 7,         /* tensor-map encoding entry point unavailable or failed        */
   GDPA_ERR_CAPACITY = 8,       /* schedule buffer too small for this batch                     */
-  GDPA_ERR_DEVICE = 9          /* current device is not compute capability 10.x               */
+  GDPA_ERR_DEVICE = 9,         /* current device is not compute capability 10.x               */
+  GDPA_ERR_NOALLOC_TOO_LARGE = 10 /* gdpa_fwd_noalloc: batch needs more than GDPA_NOALLOC_MAX_ITEMS */
 };
 
 /* Activation ids.  0..11 are the reference's enumeration order
@@ -149,6 +150,20 @@ typedef struct GdpaFwdParams {
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
+
+/* Forward for callers that cannot allocate device memory.  No counterpart in the reference, whose
+ * Python host code allocates freely through torch.  Same contract as gdpa_fwd() except that
+ * `schedule` is ignored: the work schedule is built into a fixed array inside the library's device
+ * image, so the caller passes only inputs and outputs.  Meant for hosts that own all device memory
+ * through an arena of their own, or that run where an allocation would stall the device.
+ *  - Limit: heads * (total_q / 256 + batch) <= GDPA_NOALLOC_MAX_ITEMS, otherwise
+ *    GDPA_ERR_NOALLOC_TOO_LARGE is returned and nothing is launched.
+ *  - The array (1 MiB) is shared by every call on a device and keeps the previous call's contents;
+ *    calls whose kernels may overlap on the GPU race on it and must be ordered by the caller.
+ *  - The first call on a device resolves the array's address; make it before any stream capture.
+ *  - Calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define GDPA_NOALLOC_MAX_ITEMS 65536
+int gdpa_fwd_noalloc(const GdpaFwdParams* params, gdpa_stream_t stream);
 
 /* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule
