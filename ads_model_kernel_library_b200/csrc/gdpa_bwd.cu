@@ -519,8 +519,5 @@ int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStre
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 
-// Softmax and FP8 forward live in their own translation units once built.
-int launch_fwd_softmax_bf16(const FwdLaunch&, int) { return GDPA_ERR_UNSUPPORTED_ACT_; }
-int launch_fwd_fp8(const FwdLaunch&, int, int) { return GDPA_ERR_UNSUPPORTED_ACT_; }
 
 }  // namespace gdpa

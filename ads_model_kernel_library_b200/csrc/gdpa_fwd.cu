@@ -46,16 +46,20 @@ enum FwdBar : int {
   B_P_FULL = 6 + 2 * kKvStages,        // [2] activation group (128 arrivals) -> MMA
   B_O_FULL = 8 + 2 * kKvStages,        // [2] MMA commit -> epilogue
   B_O_EMPTY = 10 + 2 * kKvStages,      // [2] epilogue (128 arrivals) -> MMA
-  B_COUNT = 12 + 2 * kKvStages
+  B_L_FULL = 12 + 2 * kKvStages,       // [2] softmax: activation group (128 arrivals) -> epilogue (row sums)
+  B_COUNT = 14 + 2 * kKvStages
 };
 
-template <int D>
+template <int D, int EB>
 struct FwdSmem {
-  static constexpr int kTileBytes = kTile * D * 2;       // one 128 x D bf16 tile
-  static constexpr int kHalfBytes = kTile * 64 * 2;      // one 128 x 64 swizzled box
+  static constexpr int kTileBytes = kTile * D * EB;      // one 128 x D tile of EB-byte elements
+  static constexpr int kHalfBytes = kTile * 128;         // one swizzled box: 128 rows x 128 bytes
+  static constexpr int kBoxes = D * EB / 128;            // boxes per tile
+  static constexpr int kBoxCols = 128 / EB;              // elements per box row
   static constexpr int kQOff = 0;
   static constexpr int kKvOff = 2 * kTileBytes;
-  static constexpr int kBarOff = kKvOff + kKvStages * kTileBytes;
+  static constexpr int kRowSumOff = kKvOff + kKvStages * kTileBytes;  // softmax: float[2][128]
+  static constexpr int kBarOff = kRowSumOff + 2 * kTile * 4;
   static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kBytes = kAbortOff + 4;
@@ -66,11 +70,13 @@ struct FwdSmem {
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
     goto role_done;
 
-template <int D, int ACT>
+template <int D, int ACT, bool FP8>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
-  using L = FwdSmem<D>;
+  constexpr int EB = FP8 ? 1 : 2;
+  constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
+  using L = FwdSmem<D, EB>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -84,7 +90,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < B_COUNT; ++i) {
-      const bool many = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2);
+      const bool many = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2) ||
+                        (i >= B_L_FULL && i < B_L_FULL + 2);
       mbar_init(bar_base + 8u * i, many ? 128u : 1u);
     }
     *abort_flag = 0;
@@ -105,10 +112,12 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_ptr;
   const int n_items = a.sched[0];
 
+  // Operand format code: 1 = bf16 for kind::f16, 0 = e4m3 for kind::f8f6f4.
+  constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   // QK: A = Q tile (K-major), B = K tile (K-major), M = 128, N = 128.
-  constexpr uint32_t kIdescQK = umma_idesc(1, 1, 0, 0, kTile, kTile);
+  constexpr uint32_t kIdescQK = umma_idesc(kFmt, kFmt, 0, 0, kTile, kTile);
   // PV: A = P in TMEM, B = V tile (MN-major: head dim contiguous), M = 128, N = D.
-  constexpr uint32_t kIdescPV = umma_idesc(1, 1, 0, 1, kTile, D);
+  constexpr uint32_t kIdescPV = umma_idesc(kFmt, kFmt, 0, 1, kTile, D);
 
   if (warp >= 12) {
    setmaxnreg_dec<kFwdRegsOther>();
@@ -136,9 +145,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t bar = bar_base + 8u * (B_Q_FULL + s);
             mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-            for (int hf = 0; hf < D / 64; ++hf)
-              tma_load_3d(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, w.h,
-                          q_row + s * kTile);
+            for (int hf = 0; hf < L::kBoxes; ++hf)
+              tma_load_3d(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * L::kBoxCols,
+                          w.h, q_row + s * kTile);
           } else {
             const int t = (step == 1) ? 0 : step - 2;  // 0 = K0, 1 = V0, 2 = K1, ...
             const int j = t >> 1;
@@ -147,9 +156,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t bar = bar_base + 8u * (B_KV_FULL + kv_stage);
             mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-            for (int hf = 0; hf < D / 64; ++hf)
-              tma_load_3d(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar, hf * 64,
-                          w.h, kv_row + j * kTile);
+            for (int hf = 0; hf < L::kBoxes; ++hf)
+              tma_load_3d(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar,
+                          hf * L::kBoxCols, w.h, kv_row + j * kTile);
             if (++kv_stage == kKvStages) {
               kv_stage = 0;
               kv_phase ^= 1u;
@@ -166,20 +175,26 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_qk = [&](int s, uint32_t k_stage) {
         const uint32_t a_base = smem_base + L::kQOff + s * L::kTileBytes;
         const uint32_t b_base = smem_base + L::kKvOff + k_stage * L::kTileBytes;
+        // one K slice = 32 bytes of the head dim (16 bf16 or 32 e4m3), four slices per 128-byte box
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
+        for (int kk = 0; kk < D * EB / 32; ++kk) {
           const uint32_t off = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
-          umma_ss_f16(tmem_base + s * kTile, umma_smem_desc_sw128(a_base + off, 16, 1024),
-                      umma_smem_desc_sw128(b_base + off, 16, 1024), kIdescQK, kk > 0 ? 1u : 0u);
+          const uint64_t da = umma_smem_desc_sw128(a_base + off, 16, 1024);
+          const uint64_t db = umma_smem_desc_sw128(b_base + off, 16, 1024);
+          if constexpr (FP8) umma_ss_f8(tmem_base + s * kTile, da, db, kIdescQK, kk > 0 ? 1u : 0u);
+          else umma_ss_f16(tmem_base + s * kTile, da, db, kIdescQK, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int s, uint32_t v_stage, bool accumulate) {
         const uint32_t b_base = smem_base + L::kKvOff + v_stage * L::kTileBytes;
+        // one K slice = 16 (bf16) or 32 (e4m3) KV rows of 128 bytes; P holds it in 8 TMEM columns
+        constexpr int kRowsPerSlice = 32 / EB;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          umma_ts_f16(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8,
-                      umma_smem_desc_sw128(b_base + kk * 2048, L::kHalfBytes, 1024), kIdescPV,
-                      (accumulate || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
+          const uint64_t db = umma_smem_desc_sw128(b_base + kk * kRowsPerSlice * 128, L::kHalfBytes, 1024);
+          const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
+          if constexpr (FP8) umma_ts_f8(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8, db, kIdescPV, acc);
+          else umma_ts_f16(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8, db, kIdescPV, acc);
         }
       };
       WorkWalker walker(n_items);
@@ -253,6 +268,112 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int nkv = (w.lkv + kTile - 1) / kTile;
       const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
       if (nkv == 0 || s >= nst) continue;
+      if constexpr (kSoftmax) {
+        // ---- softmax with online rescaling: P = exp2(c S + bias - m), O rescaled when the running
+        // row maximum m grows by more than kThr, row sums kept in fp32 and divided out by the epilogue.
+        // FP8: c carries the Q- and K-block scales, bias = log2(V-block scale), so that P already
+        // contains the V scale and uses the whole e4m3 range; the row sum divides it out again.
+        constexpr float kThr = FP8 ? 1.f : 8.f;
+        constexpr float kPScale = FP8 ? 128.f : 1.f;
+        constexpr float kLog2e = 1.4426950408889634f;
+        float m_used = -INFINITY, row_sum = 0.f;
+        float sq = 1.f;
+        long long kv_blk0 = 0;
+        if constexpr (FP8) {
+          sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
+          kv_blk0 = load_offset(a.kv_blk_off, w.b, a.off64);
+        }
+        const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
+        for (int j = 0; j < nkv; ++j) {
+          const int valid = min(kTile, w.lkv - j * kTile);
+          float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
+          if constexpr (FP8) {
+            const float sk = a.k_scales[(kv_blk0 + j) * a.heads + w.h];
+            const float sv = a.v_scales[(kv_blk0 + j) * a.heads + w.h];
+            c *= sq * sk;
+            bias = log2f(sv);
+            inv_sv = 1.f / sv;
+          }
+          GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+          s_phase ^= 1u;
+          tc_fence_after();
+          uint32_t ra[32], rb[32];
+          // pass 1: row maximum of c * S over the valid columns
+          float rmax = -INFINITY;
+          tmem_ld32(s_tmem, ra);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t(&cur)[32] = (ch & 1) ? rb : ra;
+            uint32_t(&nxt)[32] = (ch & 1) ? ra : rb;
+            tmem_wait_ld();
+            tmem_regs_ready(cur);
+            if (ch < 3) tmem_ld32(s_tmem + (ch + 1) * 32, nxt);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float t = __uint_as_float(cur[i]) * c;
+              rmax = (ch * 32 + i < valid) ? fmaxf(rmax, t) : rmax;
+            }
+          }
+          const float m_new = fmaxf(m_used, rmax + bias);
+          if (j == 0) {
+            m_used = m_new;
+          } else if (__any_sync(0xffffffffu, m_new > m_used + kThr)) {
+            // rescale this warp's O rows (PV of the previous KV tile has completed: the commit that
+            // released this S tile was issued after it)
+            const float alpha = ex2_approx(m_used - m_new);
+            row_sum *= alpha;
+            m_used = m_new;
+#pragma unroll
+            for (int ch = 0; ch < D / 32; ++ch) {
+              tmem_ld32(o_tmem + ch * 32, ra);
+              tmem_wait_ld();
+              tmem_regs_ready(ra);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
+              tmem_st32(o_tmem + ch * 32, ra);
+            }
+          }
+          // pass 2: P = exp2(c S + bias - m), row sum, quantise, store over the S columns already read
+          const float off = bias - m_used;
+          float psum = 0.f;
+          tmem_ld32(s_tmem, ra);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t(&cur)[32] = (ch & 1) ? rb : ra;
+            uint32_t(&nxt)[32] = (ch & 1) ? ra : rb;
+            tmem_wait_ld();
+            tmem_regs_ready(cur);
+            if (ch < 3) tmem_ld32(s_tmem + (ch + 1) * 32, nxt);
+            float pv[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
+              pv[i] = (ch * 32 + i < valid) ? e : 0.f;
+              psum += pv[i];
+            }
+            if constexpr (FP8) {
+              uint32_t pk[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                pk[i] = pack_e4m3x4(pv[4 * i] * kPScale, pv[4 * i + 1] * kPScale, pv[4 * i + 2] * kPScale, pv[4 * i + 3] * kPScale);
+              tmem_st8(s_tmem + ch * 8, pk);
+            } else {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
+              tmem_st16(s_tmem + ch * 16, pk);
+            }
+          }
+          row_sum = fmaf(psum, inv_sv, row_sum);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_base + 8u * (B_P_FULL + s));
+        }
+        // hand the row sum to the epilogue (it divides O by it)
+        reinterpret_cast<float*>(smem + L::kRowSumOff)[s * kTile + (warp & 3) * 32 + lane] = row_sum * kPScale;
+        mbar_arrive(bar_base + 8u * (B_L_FULL + s));
+        continue;
+      }
       for (int j = 0; j < nkv; ++j) {
         const int valid = min(kTile, w.lkv - j * kTile);  // valid KV columns of this tile
         GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
@@ -313,6 +434,11 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           continue;
         }
         GDPA_WAIT(B_O_FULL + s, o_phase[s], ST_ROLE_EPI);
+        float inv_l = 1.f;
+        if constexpr (kSoftmax) {
+          GDPA_WAIT(B_L_FULL + s, o_phase[s], ST_ROLE_EPI);
+          inv_l = 1.f / reinterpret_cast<volatile float*>(smem + L::kRowSumOff)[s * kTile + row];
+        }
         o_phase[s] ^= 1u;
         tc_fence_after();
         const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
@@ -334,10 +460,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(cur[8 * i + 0]), __uint_as_float(cur[8 * i + 1]));
-              v.y = pack_bf16x2(__uint_as_float(cur[8 * i + 2]), __uint_as_float(cur[8 * i + 3]));
-              v.z = pack_bf16x2(__uint_as_float(cur[8 * i + 4]), __uint_as_float(cur[8 * i + 5]));
-              v.w = pack_bf16x2(__uint_as_float(cur[8 * i + 6]), __uint_as_float(cur[8 * i + 7]));
+              v.x = pack_bf16x2(__uint_as_float(cur[8 * i + 0]) * inv_l, __uint_as_float(cur[8 * i + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(cur[8 * i + 2]) * inv_l, __uint_as_float(cur[8 * i + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(cur[8 * i + 4]) * inv_l, __uint_as_float(cur[8 * i + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(cur[8 * i + 6]) * inv_l, __uint_as_float(cur[8 * i + 7]) * inv_l);
               dst[c * 4 + i] = v;
             }
           }
@@ -359,10 +485,10 @@ role_done:
 
 #undef GDPA_WAIT
 
-template <int D, int ACT>
+template <int D, int ACT, bool FP8>
 int launch_fwd_inst(const FwdLaunch& l) {
-  using L = FwdSmem<D>;
-  auto kernel = gdpa_fwd_kernel<D, ACT>;
+  using L = FwdSmem<D, FP8 ? 1 : 2>;
+  auto kernel = gdpa_fwd_kernel<D, ACT, FP8>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
   kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
@@ -372,14 +498,15 @@ int launch_fwd_inst(const FwdLaunch& l) {
 template <int D>
 int launch_fwd_d(const FwdLaunch& l, int act_class) {
   switch (act_class) {
-    case ACT_RAW: return launch_fwd_inst<D, ACT_RAW>(l);
-    case ACT_GELU_ERF: return launch_fwd_inst<D, ACT_GELU_ERF>(l);
-    case ACT_GELU_TANH: return launch_fwd_inst<D, ACT_GELU_TANH>(l);
-    case ACT_LEAKY_RELU: return launch_fwd_inst<D, ACT_LEAKY_RELU>(l);
-    case ACT_RELU: return launch_fwd_inst<D, ACT_RELU>(l);
-    case ACT_SILU: return launch_fwd_inst<D, ACT_SILU>(l);
-    case ACT_HARDSWISH: return launch_fwd_inst<D, ACT_HARDSWISH>(l);
-    case ACT_RELU_SQUARE: return launch_fwd_inst<D, ACT_RELU_SQUARE>(l);
+    case ACT_RAW: return launch_fwd_inst<D, ACT_RAW, false>(l);
+    case ACT_GELU_ERF: return launch_fwd_inst<D, ACT_GELU_ERF, false>(l);
+    case ACT_GELU_TANH: return launch_fwd_inst<D, ACT_GELU_TANH, false>(l);
+    case ACT_LEAKY_RELU: return launch_fwd_inst<D, ACT_LEAKY_RELU, false>(l);
+    case ACT_RELU: return launch_fwd_inst<D, ACT_RELU, false>(l);
+    case ACT_SILU: return launch_fwd_inst<D, ACT_SILU, false>(l);
+    case ACT_HARDSWISH: return launch_fwd_inst<D, ACT_HARDSWISH, false>(l);
+    case ACT_RELU_SQUARE: return launch_fwd_inst<D, ACT_RELU_SQUARE, false>(l);
+    case ACT_SOFTMAX: return launch_fwd_inst<D, ACT_SOFTMAX, false>(l);
     default: return GDPA_ERR_UNSUPPORTED_ACT_;
   }
 }
@@ -390,6 +517,15 @@ int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class) {
   if (head_dim == 128) return launch_fwd_d<128>(l, act_class);
   if (head_dim == 64) return launch_fwd_d<64>(l, act_class);
   return GDPA_ERR_UNSUPPORTED_DIM_;
+}
+
+int launch_fwd_softmax_bf16(const FwdLaunch& l, int head_dim) { return launch_fwd_bf16(l, head_dim, ACT_SOFTMAX); }
+
+// FP8 e4m3 operands: softmax only, head_dim 128 only (a 64-byte row would need the 64-byte swizzle).
+int launch_fwd_fp8(const FwdLaunch& l, int head_dim, int act_class) {
+  if (act_class != ACT_SOFTMAX) return GDPA_ERR_UNSUPPORTED_ACT_;
+  if (head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM_;
+  return launch_fwd_inst<128, ACT_SOFTMAX, true>(l);
 }
 
 }  // namespace gdpa
