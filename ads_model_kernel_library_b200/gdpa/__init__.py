@@ -8,5 +8,5 @@ from .ops import (  # noqa: F401
     kernel_timing,
     quantize_fp8_blockwise,
 )
-from .sharding import plan_token_balanced_shards, shard_jagged  # noqa: F401
+from .sharding import gather_rows, max_over_ranks, plan_token_balanced_shards, shard_inputs, shard_jagged  # noqa: F401
 from .workloads import WORKLOADS, make_workload, useful_flops  # noqa: F401

@@ -55,3 +55,45 @@ def shard_jagged(offsets, start: int, end: int):
     row_start = int(offsets[start])
     row_end = int(offsets[end])
     return row_start, row_end, offsets[start:end + 1] - row_start
+
+
+def shard_inputs(q, k, v, q_offsets, kv_offsets, rank: int, world: int, balance: str = "tokens"):
+    """Slice a jagged batch for one rank: returns ``(q_r, k_r, v_r, q_off_r, kv_off_r, (seq_start,
+    seq_end), (q_row_start, q_row_end))`` with offsets rebased to zero.  Works on torch tensors on any
+    device; the offsets are read on the host once (planning is host logic)."""
+    qo = q_offsets.detach().cpu().numpy().astype(np.int64)
+    ko = kv_offsets.detach().cpu().numpy().astype(np.int64)
+    shards = plan_token_balanced_shards(np.diff(qo), np.diff(ko), world, balance)
+    s, e = shards[rank]
+    q0, q1 = int(qo[s]), int(qo[e])
+    k0, k1 = int(ko[s]), int(ko[e])
+    return (q[q0:q1], k[k0:k1], v[k0:k1], q_offsets[s:e + 1] - q0, kv_offsets[s:e + 1] - k0, (s, e), (q0, q1))
+
+
+def gather_rows(local, group=None):
+    """All-gather row-sharded tensors of different lengths (validation only; the hot path has no
+    collective).  Returns the concatenation in rank order on every rank."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    n = torch.tensor([local.shape[0]], dtype=torch.int64, device=local.device)
+    counts = [torch.zeros_like(n) for _ in range(world)]
+    dist.all_gather(counts, n, group=group)
+    counts = [int(c.item()) for c in counts]
+    mx = max(counts) if counts else 0
+    pad = torch.zeros((mx,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    pad[: local.shape[0]] = local
+    bufs = [torch.empty_like(pad) for _ in range(world)]
+    dist.all_gather(bufs, pad, group=group)
+    return torch.cat([b[:c] for b, c in zip(bufs, counts)], dim=0)
+
+
+def max_over_ranks(value: float, device, group=None) -> float:
+    """Maximum of a per-rank scalar (device-timed step duration) over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t.item())

@@ -62,7 +62,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -196,6 +196,9 @@ def main():
 
     w = make_workload(args.workload, batch=args.batch)
     strong = args.workload == "c5_zipf_sharded"
+    fp8 = args.workload == "c4_fp8_softmax"
+    fwd_only = w.mode == "fwd"
+    metric = METRIC if not fwd_only else "gdpa_fwd_useful_tflops"
     if strong:
         # token-balanced contiguous ranges; a rank's range is streamed in pieces that fit in HBM
         pieces_per_rank = max(1, 8 // world)
@@ -210,12 +213,28 @@ def main():
         t = make_tensors(w, dev, seed=1000 * rank + i, with_grad_out=True, seq_range=(s, e))
         t["lq"], t["lk"] = w.q_lens[s:e], w.kv_lens[s:e]
         t["max_q"], t["max_kv"] = int(t["lq"].max()), int(t["lk"].max())
+        if fp8:
+            # quantise once, outside the timed region: FP8 tensors + per-block scales are the op's inputs
+            t["q8"], t["sq"], t["qb"] = G.quantize_fp8_blockwise(t["q"].float(), t["q_offsets"])
+            t["k8"], t["sk"], t["kb"] = G.quantize_fp8_blockwise(t["k"].float(), t["kv_offsets"])
+            t["v8"], t["sv"], t["vb"] = G.quantize_fp8_blockwise(t["v"].float(), t["kv_offsets"])
         batches.append(t)
-    flops_rank = sum(useful_flops(b["lq"], b["lk"], w.heads, w.head_dim, "fwd_bwd") for b in batches)
+    flops_rank = sum(useful_flops(b["lq"], b["lk"], w.heads, w.head_dim, w.mode) for b in batches)
     tokens_rank = sum(int(b["lq"].sum() + b["lk"].sum()) for b in batches)
 
     def step():
         for b in batches:
+            if fwd_only:
+                with torch.no_grad():
+                    if fp8:
+                        G.generalized_dot_product_attention_fp8(b["q8"], b["k8"], b["v8"], b["sq"], b["sk"], b["sv"], b["qb"],
+                                                                b["kb"], b["q_offsets"], b["kv_offsets"], b["max_q"],
+                                                                b["max_kv"], qk_scale=w.qk_scale, activation=w.activation)
+                    else:
+                        G.generalized_dot_product_attention(b["q"], b["k"], b["v"], b["q_offsets"], b["kv_offsets"],
+                                                            b["max_q"], b["max_kv"], qk_scale=w.qk_scale,
+                                                            activation=w.activation)
+                continue
             q = b["q"].requires_grad_(True)
             k = b["k"].requires_grad_(True)
             v = b["v"].requires_grad_(True)
@@ -264,24 +283,32 @@ def main():
     assert G.kernel_status() == 0, "a kernel wait ran out during the timed region"
 
     # dominant kernel: the backward kernel (last call of each step carries the events)
-    bwd_ms = float(np.mean([a.elapsed_time(b) for a, b in bwd_ev]))
     fwd_ms = float(np.mean([a.elapsed_time(b) for a, b in fwd_ev]))
     last = batches[-1]
-    bwd_flops = useful_flops(last["lq"], last["lk"], w.heads, w.head_dim, "bwd")
     fwd_flops = useful_flops(last["lq"], last["lk"], w.heads, w.head_dim, "fwd")
     peaks = _peaks()
     peak = peaks["bf16_tflops_sustained"]
-    achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "gdpa_bwd_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "peak_source": peaks["source"] + " bf16_tflops_sustained (kernel timed inside a long step)",
-                "traffic": None, "kernel_ms": bwd_ms,
-                "fwd_kernel": {"kernel": "gdpa_fwd_kernel", "achieved": fwd_flops / (fwd_ms * 1e-3) / 1e12,
-                               "frac": fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, "kernel_ms": fwd_ms},
-                "frac_of_nominal_2250": achieved / 2250.0}
+    fwd_part = {"kernel": "gdpa_fwd_kernel", "achieved": fwd_flops / (fwd_ms * 1e-3) / 1e12,
+                "frac": fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, "kernel_ms": fwd_ms}
+    if fwd_only:
+        peak_note = peaks["source"] + " bf16_tflops_sustained"
+        if fp8:
+            peak_note += " (no measured FP8 rate on this pool: the bf16 rate is the denominator, nominal FP8 is 2x bf16)"
+        roofline = {"bound": "tensor", "kernel": "gdpa_fwd_kernel", "achieved": fwd_part["achieved"], "peak": peak,
+                    "unit": "TFLOP/s", "frac": fwd_part["frac"], "peak_source": peak_note, "traffic": None,
+                    "kernel_ms": fwd_ms, "frac_of_nominal": fwd_part["achieved"] / (4500.0 if fp8 else 2250.0)}
+    else:
+        bwd_ms = float(np.mean([a.elapsed_time(b) for a, b in bwd_ev]))
+        bwd_flops = useful_flops(last["lq"], last["lk"], w.heads, w.head_dim, "bwd")
+        achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "gdpa_bwd_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                    "frac": achieved / peak,
+                    "peak_source": peaks["source"] + " bf16_tflops_sustained (kernel timed inside a long step)",
+                    "traffic": None, "kernel_ms": bwd_ms, "fwd_kernel": fwd_part, "frac_of_nominal_2250": achieved / 2250.0}
 
     # ---- end to end: pinned host buffers, H2D of the inputs and D2H of every result per step ----
     e2e = None
-    if not args.no_e2e and not strong:
+    if not args.no_e2e and not strong and not fwd_only:
         b = batches[0]
         host_in = {n: b[n].detach().cpu().pin_memory() for n in ("q", "k", "v", "do")}
         host_out = {n: torch.empty_like(host_in["q" if n in ("o", "dq") else "k"]).pin_memory() for n in ("o", "dq", "dk", "dv")}
@@ -318,16 +345,16 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, dt, cores, sample = _cpu_oracle_rate(args.workload if not strong else DEFAULT_WORKLOAD)
+        v, dt, cores, sample = _cpu_oracle_rate(DEFAULT_WORKLOAD if (strong or fwd_only) else args.workload)
         cpu_baseline = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": int(sum(len(b["lq"]) for b in batches)), "heads": w.heads,
-                       "head_dim": w.head_dim, "activation": w.activation, "pass": "fwd+bwd",
+                       "head_dim": w.head_dim, "activation": w.activation, "pass": "fwd" if fwd_only else "fwd+bwd",
                        "tokens_per_step": int(total_tokens), "useful_tflop_per_step": total_flops / 1e12,
                        "l2": "inputs larger than L2 (each of Q, K, V, dO exceeds 126 MB), no flush",
                        "parallelism": f"batch sharded by sequence over {world} GPU(s), no collective"},
