@@ -12,6 +12,7 @@ namespace gdpa {
 namespace {
 
 std::atomic<long long> g_launches{0};
+std::atomic<long long*> g_trace{nullptr};
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -113,6 +114,8 @@ const char* gdpa_strerror(int code) {
 
 int32_t gdpa_version(void) { return 100; }
 
+void gdpa_debug_set_trace(void* device_buffer) { g_trace.store(static_cast<long long*>(device_buffer)); }
+
 int64_t gdpa_launch_count(void) { return g_launches.load(); }
 
 size_t gdpa_schedule_bytes(int32_t mode, int64_t total_rows, int32_t batch, int32_t heads) {
@@ -189,6 +192,7 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.scale = p->qk_scale;
   l.args.sched = static_cast<const int*>(p->schedule);
   l.args.status = p->status;
+  l.args.trace = g_trace.load();
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -266,6 +270,7 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.scale = p->qk_scale;
   l.args.sched = static_cast<const int*>(p->schedule);
   l.args.status = p->status;
+  l.args.trace = g_trace.load();
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;

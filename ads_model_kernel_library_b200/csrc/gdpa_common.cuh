@@ -42,6 +42,15 @@ __device__ __forceinline__ long long load_offset(const void* p, int i, int is64)
   return is64 ? static_cast<const long long*>(p)[i] : static_cast<long long>(static_cast<const int*>(p)[i]);
 }
 
+// Cycle stamps for performance analysis: CTA 0 writes clock64() into slot `slot` of the trace buffer
+// when one was registered with gdpa_debug_set_trace(); otherwise a single predicated-off store.
+constexpr int kTraceSlots = 16384;
+#define GDPA_TRACE(args, slot)                                                                  \
+  do {                                                                                          \
+    if ((args).trace != nullptr && blockIdx.x == 0 && (slot) >= 0 && (slot) < kTraceSlots)     \
+      (args).trace[(slot)] = clock64();                                                         \
+  } while (0)
+
 // One work item of a schedule, with the sequence geometry it refers to.
 struct Work {
   int b, h, blk;
@@ -117,6 +126,10 @@ __device__ __forceinline__ float act_scaled(float x, float scale, float hscale) 
 
 // Two activations at once, packed bf16x2 result (x0 in the low half).  GELU-tanh and SiLU use packed
 // f32x2 arithmetic around the two MUFU evaluations; the other classes fall back to the scalar form.
+// Measured on B200: tanh.approx.f32 issues at half the rate of ex2 / rcp (16 cycles per warp
+// instruction and SM sub-partition), the two-value tanh.approx.f16x2 is no faster per element, and
+// sigmoid built from ex2 plus a Newton reciprocal on the FMA pipe costs more issue slots than it saves
+// MUFU cycles; the plain f32 tanh below was the fastest of the three.
 template <int ACT>
 __device__ __forceinline__ uint32_t act_scaled_pair_bf16(float x0, float x1, float scale, float hscale) {
   if constexpr (ACT == ACT_GELU_TANH) {

@@ -172,29 +172,33 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       uint32_t kv_stage = 0, kv_phase = 0;
       uint32_t q_phase[2] = {0, 0}, p_phase[2] = {0, 0}, o_phase[2] = {0, 0};
+      int tr = 0;
+      // Descriptors of stage 0 / ring slot 0, built once; per MMA only the low word moves.
+      const uint64_t dq0 = umma_smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+      const uint64_t dk0 = umma_smem_desc_sw128(smem_base + L::kKvOff, 16, 1024);
+      const uint64_t dv0 = umma_smem_desc_sw128(smem_base + L::kKvOff, L::kHalfBytes, 1024);
       auto issue_qk = [&](int s, uint32_t k_stage) {
-        const uint32_t a_base = smem_base + L::kQOff + s * L::kTileBytes;
-        const uint32_t b_base = smem_base + L::kKvOff + k_stage * L::kTileBytes;
+        const uint64_t da = umma_desc_advance(dq0, s * L::kTileBytes);
+        const uint64_t db = umma_desc_advance(dk0, k_stage * L::kTileBytes);
+        const uint32_t d_tmem = tmem_base + s * kTile;
         // one K slice = 32 bytes of the head dim (16 bf16 or 32 e4m3), four slices per 128-byte box
 #pragma unroll
         for (int kk = 0; kk < D * EB / 32; ++kk) {
           const uint32_t off = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
-          const uint64_t da = umma_smem_desc_sw128(a_base + off, 16, 1024);
-          const uint64_t db = umma_smem_desc_sw128(b_base + off, 16, 1024);
-          if constexpr (FP8) umma_ss_f8(tmem_base + s * kTile, da, db, kIdescQK, kk > 0 ? 1u : 0u);
-          else umma_ss_f16(tmem_base + s * kTile, da, db, kIdescQK, kk > 0 ? 1u : 0u);
+          if constexpr (FP8) umma_ss_f8(d_tmem, umma_desc_advance(da, off), umma_desc_advance(db, off), kIdescQK, kk > 0 ? 1u : 0u);
+          else umma_ss_f16(d_tmem, umma_desc_advance(da, off), umma_desc_advance(db, off), kIdescQK, kk > 0 ? 1u : 0u);
         }
       };
       auto issue_pv = [&](int s, uint32_t v_stage, bool accumulate) {
-        const uint32_t b_base = smem_base + L::kKvOff + v_stage * L::kTileBytes;
+        const uint64_t db = umma_desc_advance(dv0, v_stage * L::kTileBytes);
+        const uint32_t d_tmem = tmem_base + 256 + s * kTile, a_tmem = tmem_base + s * kTile;
         // one K slice = 16 (bf16) or 32 (e4m3) KV rows of 128 bytes; P holds it in 8 TMEM columns
         constexpr int kRowsPerSlice = 32 / EB;
 #pragma unroll
         for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
-          const uint64_t db = umma_smem_desc_sw128(b_base + kk * kRowsPerSlice * 128, L::kHalfBytes, 1024);
           const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
-          if constexpr (FP8) umma_ts_f8(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8, db, kIdescPV, acc);
-          else umma_ts_f16(tmem_base + 256 + s * kTile, tmem_base + s * kTile + kk * 8, db, kIdescPV, acc);
+          if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + kk * 8, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
+          else umma_ts_f16(d_tmem, a_tmem + kk * 8, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
         }
       };
       WorkWalker walker(n_items);
@@ -227,7 +231,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (more) { if (++kv_stage == kKvStages) { kv_stage = 0; kv_phase ^= 1u; } }
           GDPA_WAIT(B_KV_FULL + v_stage, v_phase, ST_ROLE_MMA);
           for (int s = 0; s < nst; ++s) {
+            GDPA_TRACE(a, tr * 32 + 16 + s * 4 + 0);
             GDPA_WAIT(B_P_FULL + s, p_phase[s], ST_ROLE_MMA);
+            GDPA_TRACE(a, tr * 32 + 16 + s * 4 + 1);
             p_phase[s] ^= 1u;
             if (j == 0) {
               GDPA_WAIT(B_O_EMPTY + s, o_phase[s] ^ 1u, ST_ROLE_MMA);
@@ -246,7 +252,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             } else {
               tc_commit(bar_base + 8u * (B_O_FULL + s));
             }
+            GDPA_TRACE(a, tr * 32 + 16 + s * 4 + 2);
           }
+          ++tr;
           tc_commit(bar_base + 8u * (B_KV_EMPTY + v_stage));
           if (more) tc_commit(bar_base + 8u * (B_KV_EMPTY + k_stage));
         }
@@ -261,6 +269,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t s_tmem = tmem_base + lane_base + s * kTile;
     const float scale = a.scale, hscale = 0.5f * a.scale;
     uint32_t s_phase = 0;
+    int tr = 0;  // trace: KV blocks seen so far by this role (slot layout: see GDPA_TRACE uses)
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
@@ -376,9 +385,11 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       for (int j = 0; j < nkv; ++j) {
         const int valid = min(kTile, w.lkv - j * kTile);  // valid KV columns of this tile
+        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
         GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
+        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 1);
         // Four 32-column chunks; the TMEM load of chunk c+1 is in flight while chunk c is computed.
         uint32_t ra[32], rb[32];
         tmem_ld32(s_tmem, ra);
@@ -404,9 +415,12 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           tmem_st16(s_tmem + c * 16, pk);
         }
+        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 2);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_base + 8u * (B_P_FULL + s));
+        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 3);
+        ++tr;
       }
     }
   } else {

@@ -31,6 +31,7 @@ struct FwdArgs {
   const float* v_scales;
   const void* q_blk_off;
   const void* kv_blk_off;
+  long long* trace;  // optional cycle-stamp buffer of CTA 0 (performance analysis); null in normal use
 };
 
 struct FwdLaunch {
@@ -53,6 +54,7 @@ struct BwdArgs {
   float scale;
   const int* sched;
   int* status;
+  long long* trace;  // optional cycle-stamp buffer of CTA 0; null in normal use
 };
 
 struct BwdLaunch {

@@ -198,6 +198,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// A descriptor is cheap to step: tiles sit below 256 KB of shared memory, so moving the start
+// address by `byte_offset` (a multiple of 16) only adds to the low word.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t byte_offset) {
+  uint32_t lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(desc));
+  lo += byte_offset >> 4;
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+
 // 32-bit instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
 // Bits: 4-5 accumulator format (1 = f32), 7-9 A format, 10-12 B format, 15 A major
 // (0 = K-major, 1 = MN-major), 16 B major, 17-22 N >> 3, 24-28 M >> 4.

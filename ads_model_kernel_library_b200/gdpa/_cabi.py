@@ -30,6 +30,7 @@ EXPORTS = (
     "gdpa_strerror",
     "gdpa_launch_count",
     "gdpa_version",
+    "gdpa_debug_set_trace",
 )
 
 
@@ -138,6 +139,8 @@ def _load() -> C.CDLL:
     lib.gdpa_strerror.argtypes = [C.c_int]
     lib.gdpa_launch_count.restype = C.c_int64
     lib.gdpa_launch_count.argtypes = []
+    lib.gdpa_debug_set_trace.restype = None
+    lib.gdpa_debug_set_trace.argtypes = [C.c_void_p]
     lib.gdpa_version.restype = C.c_int32
     lib.gdpa_version.argtypes = []
     return lib

@@ -165,6 +165,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the number of sequences (reduced-size runs)")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-flops", type=float, default=None, help="useful FLOPs of the CPU sample per step of the reference arm")
@@ -195,6 +196,8 @@ def main():
     from ads_model_kernel_library_b200.gdpa.workloads import make_tensors, make_workload, useful_flops
 
     w = make_workload(args.workload, batch=args.batch)
+    if args.activation:
+        w.activation = args.activation
     strong = args.workload == "c5_zipf_sharded"
     fp8 = args.workload == "c4_fp8_softmax"
     fwd_only = w.mode == "fwd"

@@ -220,6 +220,12 @@ const char* gdpa_strerror(int code);
  * Used by benchmarks to report how many of this library's kernels ran in a timed region. */
 int64_t gdpa_launch_count(void);
 
+/* Diagnostic hook for performance analysis: register a device buffer of 16384 int64 slots into which
+ * CTA 0 of the forward / backward kernels writes SM cycle stamps at fixed points of its pipeline
+ * (slot layout in csrc/gdpa_fwd.cu and csrc/gdpa_bwd.cu), or null to switch tracing off (default).
+ * Process-wide; not meant for production use. */
+void gdpa_debug_set_trace(void* device_buffer);
+
 /* Library version: major * 10000 + minor * 100 + patch. */
 int32_t gdpa_version(void);
 

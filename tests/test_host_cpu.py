@@ -20,7 +20,7 @@ def cabi():
 
 def test_library_exports_every_symbol_the_header_declares(cabi):
     hdr = open(os.path.join(ROOT, "include", "gdpa_b200.h")).read()
-    declared = set(re.findall(r"^\s*(?:int|size_t|const char\*|int64_t|int32_t)\s+(gdpa_\w+)\s*\(", hdr, re.M))
+    declared = set(re.findall(r"^\s*(?:int|size_t|const char\*|int64_t|int32_t|void)\s+(gdpa_\w+)\s*\(", hdr, re.M))
     assert declared, "no declarations parsed"
     assert declared == set(cabi.EXPORTS)
     for name in declared:
