@@ -9,10 +9,11 @@
 //   S^T  = K Q_m^T          (smem x smem)        -> TMEM [0,128)
 //   dP^T = V dO_m^T         (smem x smem)        -> TMEM [128,256)
 //   dV  += P^T dO_m         (P^T bf16 in TMEM, overwriting S^T)  -> TMEM [256,256+D)
-//   dK  += dS^T Q_m         (dS^T bf16 in smem)  -> TMEM [384,384+D)
-//   dQ_m = dS K             (same smem tile read MN-major)       -> TMEM [128,128+D), aliasing dP^T
+//   dK  += dS^T Q_m         (dS^T bf16 in TMEM, overwriting dP^T)  -> TMEM [384,384+D)
+//   dQ_m = dS K             (dS^T bf16 in smem, read MN-major)   -> TMEM [128,128+D), aliasing dP^T
 //
-// issued in the order S(m), dQ(m-1), dK(m-1), dP(m), dV(m) so that the element-wise work of tile m
+// issued in the order S(m), dK(m-1), dQ(m-1), dP(m), dV(m) (dK reads dS^T from TMEM, where it sits
+// over the dP^T columns that dQ then overwrites) so that the element-wise work of tile m
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
 // dQ tiles are drained by a dedicated warpgroup into shared memory and added into an fp32
 // accumulator by TMA reduce-add (32-column slabs, two staging buffers); a second kernel rounds the
@@ -37,8 +38,8 @@ namespace {
 constexpr int kBwdThreads = 16 * 32;
 constexpr int kBwdMmaWarp = 12;
 constexpr int kBwdLoadWarp = 13;
-constexpr int kRegsCompute = 168;
-constexpr int kRegsReduce = 96;
+constexpr int kRegsCompute = 144;
+constexpr int kRegsReduce = 144;
 constexpr int kRegsOther = 80;
 constexpr int kDqWarpSlabBytes = 32 * 32 * 4;  // one warp's staging slab: 32 rows x 32 fp32
 
@@ -78,6 +79,14 @@ struct BwdSmem {
   static constexpr int kBytes = kAbortOff + 4;
   static constexpr int kDynBytes = kBytes + 1024;
 };
+
+// How dQ tiles leave the SM: staged in shared memory and added by TMA reduce (full 128-byte lines at
+// L2, but 128 KB of shared-memory traffic per tile), or straight from registers with vector reductions.
+constexpr bool kDqViaTma = true;  // measured: 793 vs 578 TFLOP/s (backward, B=512 uniform workload)
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
@@ -190,6 +199,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) {
         uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase = 0, st = 0;
         uint32_t p_phase = 0, ds_phase = 0, dqe_phase = 0, dkve_phase = 0;
+        int tr = 0;  // trace: Q tiles seen so far (slot layout: tr * 32 + event, events 0-7 MMA, 8-12 element-wise, 13-16 reduce)
         const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff, sDs = smem_base + L::kDsOff;
         // A, B K-major over the head dim: D / 16 slices.
         auto mma_kmajor_pair = [&](uint32_t d_col, uint32_t a_base, uint32_t b_base) {
@@ -212,11 +222,13 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t sQ = smem_base + L::kQOff + st * L::kTileBytes;
             const uint32_t sDo = smem_base + L::kDoOff;
             if (m < nq) {
+              GDPA_TRACE(a, tr * 32 + 0);
               GDPA_WAIT(BB_Q_FULL + st, q_phase[st], ST_ROLE_MMA);
               q_phase[st] ^= 1u;
               tc_fence_after();
               mma_kmajor_pair(kColS, sK, sQ);  // S^T = K Q_m^T
               tc_commit(bar_base + 8u * BB_S_FULL);
+              GDPA_TRACE(a, tr * 32 + 1);
             }
             if (m > 0) {
               const uint32_t pst = st ^ 1u;
@@ -224,21 +236,22 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               GDPA_WAIT(BB_DS_FULL, ds_phase, ST_ROLE_MMA);
               ds_phase ^= 1u;
               tc_fence_after();
-              // dQ_{m-1} = dS K : A = dS^T tile read MN-major, B = K tile MN-major, 8 slices of 16 KV rows
+              GDPA_TRACE(a, tr * 32 + 2);
+              // dK += dS^T Q_{m-1} : A = dS^T (bf16 in TMEM over the dP^T columns this half has read),
+              // B = Q tile MN-major.  Issued before dQ, which overwrites those columns.
+#pragma unroll
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            (m > 1 || kk > 0) ? 1u : 0u);
+              // dQ_{m-1} = dS K : A = dS^T tile in shared memory read MN-major, B = K tile MN-major
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
                 umma_ss_f16(tmem_base + kColDP, umma_smem_desc_sw128(sDs + kk * 2048, L::kHalfBytes, 1024),
                             umma_smem_desc_sw128(sK + kk * 2048, L::kHalfBytes, 1024), kIdescMM, kk > 0 ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DQ_FULL);
-              // dK += dS^T Q_{m-1} : A = dS^T K-major over q, B = Q tile MN-major
-#pragma unroll
-              for (int kk = 0; kk < kTile / 16; ++kk) {
-                const uint32_t aoff = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
-                umma_ss_f16(tmem_base + kColDK, umma_smem_desc_sw128(sDs + aoff, 16, 1024),
-                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
-                            (m > 1 || kk > 0) ? 1u : 0u);
-              }
               tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
+              GDPA_TRACE(a, tr * 32 + 3);
             }
             if (m < nq) {
               GDPA_WAIT(BB_DO_FULL, do_phase, ST_ROLE_MMA);
@@ -246,10 +259,13 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               GDPA_WAIT(BB_DQ_EMPTY, dqe_phase ^ 1u, ST_ROLE_MMA);
               dqe_phase ^= 1u;
               tc_fence_after();
+              GDPA_TRACE(a, tr * 32 + 4);
               mma_kmajor_pair(kColDP, sV, sDo);  // dP^T = V dO_m^T
               tc_commit(bar_base + 8u * BB_DP_FULL);
+              GDPA_TRACE(a, tr * 32 + 5);
               GDPA_WAIT(BB_P_FULL, p_phase, ST_ROLE_MMA);
               p_phase ^= 1u;
+              GDPA_TRACE(a, tr * 32 + 6);
               if (m == 0) {
                 GDPA_WAIT(BB_DKV_EMPTY, dkve_phase ^ 1u, ST_ROLE_MMA);
                 dkve_phase ^= 1u;
@@ -262,6 +278,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                             umma_smem_desc_sw128(sDo + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
                             (m > 0 || kk > 0) ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DO_EMPTY);
+              GDPA_TRACE(a, tr * 32 + 7);
+              ++tr;
               st ^= 1u;
             }
           }
@@ -281,6 +299,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float scale = a.scale, hscale = 0.5f * a.scale;
     uint8_t* sds_row = smem + L::kDsOff + half * L::kHalfBytes + row * 128;
     uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0;
+    int tr = 0;
+    const bool tracer = (threadIdx.x == 128);
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
@@ -306,9 +326,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const bool full = tile_rows_full && qv == kTile;
         uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
         uint32_t ra[32], rb[32];
+        if (tracer) GDPA_TRACE(a, tr * 32 + 8);
         GDPA_WAIT(BB_S_FULL, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
+        if (tracer) GDPA_TRACE(a, tr * 32 + 9);
         tmem_ld32(tS + half * 64, ra);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -336,10 +358,12 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_P_FULL);
+        if (tracer) GDPA_TRACE(a, tr * 32 + 10);
 
         GDPA_WAIT(BB_DP_FULL, dp_phase, ST_ROLE_ACT);
         dp_phase ^= 1u;
         tc_fence_after();
+        if (tracer) GDPA_TRACE(a, tr * 32 + 11);
         tmem_ld32(tDP + half * 64, ra);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -347,6 +371,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_wait_ld();
           tmem_regs_ready(cur);
           if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
+          uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint32_t d[4];
@@ -360,11 +385,20 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
             // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
             *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
+            pk[4 * j + 0] = d[0];
+            pk[4 * j + 1] = d[1];
+            pk[4 * j + 2] = d[2];
+            pk[4 * j + 3] = d[3];
           }
+          // the same values as the A operand of dK, over dP^T columns this half has already read
+          tmem_st16(tDP + half * 64 + c * 16, pk);
         }
+        tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DS_FULL);
+        if (tracer) GDPA_TRACE(a, tr * 32 + 12);
+        ++tr;
       }
       // dK / dV of this KV tile: TMEM -> bf16 -> global, rows inside the sequence only.
       GDPA_WAIT(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
@@ -397,13 +431,14 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ dQ reduce warps 0-3
-    setmaxnreg_dec<kRegsReduce>();
+    setmaxnreg_inc<kRegsReduce>();  // above the 128 registers per thread the kernel is launched with
     // Each warp drains its own 32 Q rows: TMEM -> registers -> its private staging slab (32 rows x
     // 32 fp32, 128-byte swizzled, two buffers) -> one TMA reduce-add per slab.  No cross-warp barrier.
     const uint32_t tDQ = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + kColDP;
     uint8_t* stage_row = smem + L::kDqOff + warp * (2 * kDqWarpSlabBytes) + lane * 128;
     const uint32_t stage_base = smem_base + L::kDqOff + warp * (2 * kDqWarpSlabBytes);
     uint32_t dq_phase = 0, slab = 0;
+    int tr = 0;
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
@@ -411,42 +446,60 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int nq = (w.lq + kTile - 1) / kTile;
       for (int m = 0; m < nq; ++m) {
         const int q_row0 = static_cast<int>(w.q_start) + m * kTile + warp * 32;
-        uint32_t ra[32], rb[32];
+        uint32_t r[D / 32][32];
+        if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 13);
         {
           const bool ok = mbar_wait(bar_base + 8u * BB_DQ_FULL, dq_phase, abort_flag, a.status, (BB_DQ_FULL << 8) | ST_ROLE_RED);
           if (!__all_sync(0xffffffffu, ok)) goto role_done;  // warp-uniform decision
         }
         dq_phase ^= 1u;
         tc_fence_after();
-        tmem_ld32(tDQ, ra);
+        if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 14);
+        // Pull the whole dQ tile into registers with back-to-back loads and release the TMEM columns
+        // (they alias dP^T of the next Q tile) before any staging work.
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-          tmem_wait_ld();
-          tmem_regs_ready(cur);
-          if (c < D / 32 - 1) {
-            tmem_ld32(tDQ + (c + 1) * 32, nxt);
-          } else {
-            tc_fence_before();
-            mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
-          }
-          const uint32_t buf = slab & 1u;
-          // the reduce that read this staging buffer two slabs ago must have finished reading it
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(tDQ + c * 32, r[c]);
+        tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
-                make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, w.h, q_row0);
-            tma_store_commit();
+        for (int c = 0; c < D / 32; ++c) tmem_regs_ready(r[c]);
+        tc_fence_before();
+        mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
+        if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 15);
+        if constexpr (kDqViaTma) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            const uint32_t buf = slab & 1u;
+            // the reduce that read this staging buffer two slabs ago must have finished reading it
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
+                  make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, w.h, q_row0);
+              tma_store_commit();
+            }
+            ++slab;
           }
-          ++slab;
+        } else {
+          // straight from registers: one 16-byte vector reduction per lane and 4 columns; rows beyond
+          // the sequence are skipped (their values are zero anyway)
+          const int q_local = m * kTile + warp * 32 + lane;
+          if (q_local < w.lq) {
+            float* dst = a.dq_accum + ((w.q_start + q_local) * a.heads + w.h) * static_cast<long long>(D);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c)
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(r[c][4 * j]), __uint_as_float(r[c][4 * j + 1]),
+                           __uint_as_float(r[c][4 * j + 2]), __uint_as_float(r[c][4 * j + 3]));
+          }
         }
+        if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 16);
+        ++tr;
       }
     }
   }
