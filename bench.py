@@ -35,6 +35,11 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes per Q token of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of
+# 48 sequences of the default workload, H=8, D=128; see profiles/gdpa_*_kernel_bf16_d128_gelu_small_case.md).
+# Traffic grows in proportion to the tokens, so a full launch is this figure times its Q tokens.
+NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.341e9 / 114351, "gdpa_fwd_kernel": 0.931e9 / 114351}
+
 METRIC = "gdpa_fwd_bwd_useful_tflops"
 UNIT = "TFLOP/s"
 DEFAULT_WORKLOAD = "c3_fwd_bwd_gelu_uniform"
@@ -307,7 +312,11 @@ def main():
         roofline = {"bound": "tensor", "kernel": "gdpa_bwd_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                     "frac": achieved / peak,
                     "peak_source": peaks["source"] + " bf16_tflops_sustained (kernel timed inside a long step)",
-                    "traffic": None, "kernel_ms": bwd_ms, "fwd_kernel": fwd_part, "frac_of_nominal_2250": achieved / 2250.0}
+                    "traffic": (NCU_DRAM_BYTES_PER_TOKEN["gdpa_bwd_kernel"] * float(last["lq"].sum())
+                                if (w.heads, w.head_dim) == (8, 128) else None),
+                    "traffic_note": "bytes per launch, scaled by tokens from an ncu capture of 48 sequences",
+                    "algorithmic_bytes": 16.0 * w.heads * w.head_dim * float(last["lq"].sum()),
+                    "kernel_ms": bwd_ms, "fwd_kernel": fwd_part, "frac_of_nominal_2250": achieved / 2250.0}
 
     # ---- end to end: pinned host buffers, H2D of the inputs and D2H of every result per step ----
     e2e = None
