@@ -28,13 +28,19 @@ namespace gdpa {
 
 namespace {
 
-constexpr int kFwdThreads = 16 * 32;
+// Two warp layouts.
+//  narrow (16 warps): warps 0-3 / 4-7 activation of Q tile 0 / 1 (a thread owns a whole 128-column row of
+//    S), warps 8-11 epilogue, 12 MMA, 13 TMA, 14-15 idle.  Used by softmax and FP8, whose row statistics
+//    want a whole row per thread.
+//  wide (20 warps): warps 0-7 / 8-15 activation of Q tile 0 / 1 (two warps per TMEM lane quarter, each
+//    owning 64 of the 128 S columns; they also drain their half of O at the end of a work item), 16 MMA,
+//    17 TMA, 18-19 idle; every warp keeps the 96 registers of the launch.  A single warp cannot overlap its MUFU instructions with its FMA-pipe
+//    instructions, so two activation warps per SM sub-partition and Q tile halve the activation time.
 constexpr int kFwdRegsAct = 152;
 constexpr int kFwdRegsEpi = 104;
 constexpr int kFwdRegsOther = 104;
-constexpr int kMmaWarp = 12;
-constexpr int kLoadWarp = 13;
 constexpr int kKvStages = 4;
+__host__ __device__ constexpr int fwd_threads(bool wide) { return wide ? 20 * 32 : 16 * 32; }
 
 // Barrier indices inside the shared barrier array.
 enum FwdBar : int {
@@ -70,12 +76,17 @@ struct FwdSmem {
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
     goto role_done;
 
-template <int D, int ACT, bool FP8>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+template <int D, int ACT, bool FP8, bool WIDE>
+__global__ void __launch_bounds__(fwd_threads(WIDE), 1)
 gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
+  static_assert(!(WIDE && (kSoftmax || FP8)), "the wide layout covers the element-wise bf16 activations");
+  constexpr int kActWarps = WIDE ? 16 : 8;
+  constexpr int kMmaWarp = WIDE ? 16 : 12;
+  constexpr int kLoadWarp = WIDE ? 17 : 13;
+  constexpr uint32_t kStageThreads = WIDE ? 256u : 128u;  // threads that work on one Q tile's S / O
   using L = FwdSmem<D, EB>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -92,7 +103,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int i = 0; i < B_COUNT; ++i) {
       const bool many = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2) ||
                         (i >= B_L_FULL && i < B_L_FULL + 2);
-      mbar_init(bar_base + 8u * i, many ? 128u : 1u);
+      uint32_t cnt = many ? 128u : 1u;
+      if ((i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2)) cnt = kStageThreads;
+      mbar_init(bar_base + 8u * i, cnt);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -119,8 +132,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // PV: A = P in TMEM, B = V tile (MN-major: head dim contiguous), M = 128, N = D.
   constexpr uint32_t kIdescPV = umma_idesc(kFmt, kFmt, 0, 1, kTile, D);
 
-  if (warp >= 12) {
-   setmaxnreg_dec<kFwdRegsOther>();
+  if (warp >= kMmaWarp) {
+   if constexpr (!WIDE) setmaxnreg_dec<kFwdRegsOther>();
    if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA loader
     if (lane == 0) {
@@ -197,8 +210,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
           const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
-          if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + kk * 8, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
-          else umma_ts_f16(d_tmem, a_tmem + kk * 8, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
+          // wide layout: the P slices of column half h sit at the start of that half's own S columns
+          const uint32_t a_col = WIDE ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8;
+          if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
+          else umma_ts_f16(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
         }
       };
       WorkWalker walker(n_items);
@@ -261,7 +276,100 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
    }
-  } else if (warp < 8) {
+  } else if (WIDE && warp < kActWarps) {
+    // ------------------------------------------------------------------ activation + epilogue (wide)
+    const int s = warp >> 3;           // Q tile
+    const int half = (warp >> 2) & 1;  // which 64 of the 128 S columns
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_base + s * kTile + half * 64;
+    const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile + half * (D / 2);
+    const float scale = a.scale, hscale = 0.5f * a.scale;
+    uint32_t s_phase = 0, o_phase = 0;
+    int tr = 0;
+    WorkWalker walker(n_items);
+    int idx;
+    while (walker.next(idx)) {
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const int nkv = (w.lkv + kTile - 1) / kTile;
+      const int q0 = w.blk * kFwdQBlock;
+      const int nst = (w.lq - q0 > kTile) ? 2 : 1;
+      if (s >= nst) continue;
+      const int qr = q0 + s * kTile + row;
+      const bool row_valid = qr < w.lq;
+      uint4* dst = reinterpret_cast<uint4*>(a.o + ((w.q_start + qr) * a.heads + w.h) * static_cast<long long>(D) + half * (D / 2));
+      if (nkv == 0) {
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      for (int j = 0; j < nkv; ++j) {
+        const int valid = min(kTile, w.lkv - j * kTile) - half * 64;  // valid columns among this warp's 64
+        if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
+        GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+        s_phase ^= 1u;
+        tc_fence_after();
+        if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 1);
+        uint32_t ra[32], rb[32];
+        tmem_ld32(s_tmem, ra);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t(&cur)[32] = c ? rb : ra;
+          uint32_t pk[16];
+          tmem_wait_ld();
+          tmem_regs_ready(cur);
+          if (c == 0) tmem_ld32(s_tmem + 32, rb);
+          if (valid >= (c + 1) * 32) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = act_scaled_pair_bf16<ACT>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(cur[2 * i]) : 0.f;
+              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(cur[2 * i + 1]) : 0.f;
+              pk[i] = act_scaled_pair_bf16<ACT>(x0, x1, scale, hscale);
+            }
+          }
+          tmem_st16(s_tmem + c * 16, pk);  // over columns of this half that have been read
+        }
+        if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 2);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_base + 8u * (B_P_FULL + s));
+        if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 3);
+        ++tr;
+      }
+      // epilogue: this warp's half of the O tile, TMEM -> bf16 -> global
+      GDPA_WAIT(B_O_FULL + s, o_phase, ST_ROLE_EPI);
+      o_phase ^= 1u;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t r[32];
+        tmem_ld32(o_tmem + c * 32, r);
+        tmem_wait_ld();
+        tmem_regs_ready(r);
+        if (c == D / 64 - 1) {
+          tc_fence_before();
+          mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            dst[c * 4 + i] = v;
+          }
+        }
+      }
+    }
+  } else if (!WIDE && warp < 8) {
     // ------------------------------------------------------------------ activation groups
     setmaxnreg_inc<kFwdRegsAct>();
     const int s = warp >> 2;
@@ -423,7 +531,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ++tr;
       }
     }
-  } else {
+  } else if (!WIDE) {
     // ------------------------------------------------------------------ epilogue (warps 8-11)
     setmaxnreg_dec<kFwdRegsEpi>();
     const int row = (warp & 3) * 32 + lane;
@@ -502,10 +610,11 @@ role_done:
 template <int D, int ACT, bool FP8>
 int launch_fwd_inst(const FwdLaunch& l) {
   using L = FwdSmem<D, FP8 ? 1 : 2>;
-  auto kernel = gdpa_fwd_kernel<D, ACT, FP8>;
+  constexpr bool kWide = !FP8 && ACT != ACT_SOFTMAX;
+  auto kernel = gdpa_fwd_kernel<D, ACT, FP8, kWide>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
-  kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
+  kernel<<<l.grid, fwd_threads(kWide), L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 
