@@ -74,6 +74,23 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
   return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
 }
 
+// A wait that nothing satisfies: one thread waits on an mbarrier nobody arrives on, with a short
+// limit, so that the give-up path of the kernels' bounded waits (status word written, normal return)
+// can be exercised without hanging or faulting the GPU.
+__global__ void gdpa_wait_probe_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t bar_addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(bar_addr, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) (void)mbar_wait_limit(bar_addr, 0, &abort_flag, status, 0x7700 | ST_ROLE_LOAD, limit_ns);
+  __syncthreads();
+}
+
 template <class P>
 int check_common(const P* p) {
   if (p == nullptr || p->struct_size != sizeof(P)) return GDPA_ERR_BAD_ARG;
@@ -113,6 +130,12 @@ const char* gdpa_strerror(int code) {
 }
 
 int32_t gdpa_version(void) { return 100; }
+
+int gdpa_debug_wait_probe(int32_t* status, uint64_t limit_ns, gdpa_stream_t stream) {
+  if (status == nullptr || limit_ns == 0 || limit_ns > 1000000000ull) return GDPA_ERR_BAD_ARG;
+  gdpa_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? GDPA_OK : GDPA_ERR_LAUNCH;
+}
 
 void gdpa_debug_set_trace(void* device_buffer) { g_trace.store(static_cast<long long*>(device_buffer)); }
 

@@ -82,6 +82,9 @@ struct BwdSmem {
 
 // How dQ tiles leave the SM: staged in shared memory and added by TMA reduce (full 128-byte lines at
 // L2, but 128 KB of shared-memory traffic per tile), or straight from registers with vector reductions.
+// Where the A operand of dK comes from: TMEM (32 KB less shared-memory traffic per Q tile, but dK must be
+// issued before dQ, so nothing hides the drain of dQ) or shared memory (dK runs while dQ is drained).
+constexpr bool kDkFromTmem = true;  // measured: 4 815 vs 4 957 cycles per Q tile
 constexpr bool kDqViaTma = true;  // measured: 793 vs 578 TFLOP/s (backward, B=512 uniform workload)
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -237,19 +240,31 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               ds_phase ^= 1u;
               tc_fence_after();
               GDPA_TRACE(a, tr * 32 + 2);
-              // dK += dS^T Q_{m-1} : A = dS^T (bf16 in TMEM over the dP^T columns this half has read),
-              // B = Q tile MN-major.  Issued before dQ, which overwrites those columns.
+              if constexpr (kDkFromTmem) {
+                // dK += dS^T Q_{m-1} : A = dS^T (bf16 in TMEM over the dP^T columns this half has read),
+                // B = Q tile MN-major.  Issued before dQ, which overwrites those columns.
 #pragma unroll
-              for (int kk = 0; kk < kTile / 16; ++kk)
-                umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
-                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
-                            (m > 1 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                  umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+                              umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                              (m > 1 || kk > 0) ? 1u : 0u);
+              }
               // dQ_{m-1} = dS K : A = dS^T tile in shared memory read MN-major, B = K tile MN-major
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
                 umma_ss_f16(tmem_base + kColDP, umma_smem_desc_sw128(sDs + kk * 2048, L::kHalfBytes, 1024),
                             umma_smem_desc_sw128(sK + kk * 2048, L::kHalfBytes, 1024), kIdescMM, kk > 0 ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DQ_FULL);
+              if constexpr (!kDkFromTmem) {
+                // dK += dS^T Q_{m-1} : A = dS^T in shared memory, K-major over q; runs while dQ is drained
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk) {
+                  const uint32_t aoff = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
+                  umma_ss_f16(tmem_base + kColDK, umma_smem_desc_sw128(sDs + aoff, 16, 1024),
+                              umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                              (m > 1 || kk > 0) ? 1u : 0u);
+                }
+              }
               tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
               GDPA_TRACE(a, tr * 32 + 3);
             }
@@ -391,9 +406,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[4 * j + 3] = d[3];
           }
           // the same values as the A operand of dK, over dP^T columns this half has already read
-          tmem_st16(tDP + half * 64 + c * 16, pk);
+          if constexpr (kDkFromTmem) tmem_st16(tDP + half * 64 + c * 16, pk);
         }
-        tmem_wait_st();
+        if constexpr (kDkFromTmem) tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DS_FULL);

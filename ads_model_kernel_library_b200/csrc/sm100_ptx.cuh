@@ -63,8 +63,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  Returns false if the wait ran out or another role already gave up; in the first
 // case it records `code` in *abort_flag (shared) and in *status (global, may be null).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -73,13 +73,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag != 0) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         *abort_flag = code;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // -------------------------------------------- TMA ---------------------------------------------

@@ -1,4 +1,5 @@
 """GDPA operator package: drop-in for the reference's ``gdpa`` entry point."""
+from .host_pipeline import forward_backward_host  # noqa: F401
 from .math import Activation, activation_string_to_int, activation_to_int, int_to_activation  # noqa: F401
 from .ops import (  # noqa: F401
     expect_contiguous,

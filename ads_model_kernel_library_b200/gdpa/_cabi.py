@@ -31,6 +31,7 @@ EXPORTS = (
     "gdpa_launch_count",
     "gdpa_version",
     "gdpa_debug_set_trace",
+    "gdpa_debug_wait_probe",
 )
 
 
@@ -139,6 +140,8 @@ def _load() -> C.CDLL:
     lib.gdpa_strerror.argtypes = [C.c_int]
     lib.gdpa_launch_count.restype = C.c_int64
     lib.gdpa_launch_count.argtypes = []
+    lib.gdpa_debug_wait_probe.restype = C.c_int
+    lib.gdpa_debug_wait_probe.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     lib.gdpa_debug_set_trace.restype = None
     lib.gdpa_debug_set_trace.argtypes = [C.c_void_p]
     lib.gdpa_version.restype = C.c_int32

@@ -170,6 +170,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the number of sequences (reduced-size runs)")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-chunks", type=int, default=16)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -327,18 +328,13 @@ def main():
         h2d = sum(x.numel() * x.element_size() for x in host_in.values())
         d2h = sum(x.numel() * x.element_size() for x in host_out.values())
 
+        host_off = {"q": b["q_offsets"].cpu(), "k": b["kv_offsets"].cpu()}
+
         def e2e_step():
-            q = host_in["q"].to(dev, non_blocking=True).requires_grad_(True)
-            k = host_in["k"].to(dev, non_blocking=True).requires_grad_(True)
-            v = host_in["v"].to(dev, non_blocking=True).requires_grad_(True)
-            do = host_in["do"].to(dev, non_blocking=True)
-            o = G.generalized_dot_product_attention(q, k, v, b["q_offsets"], b["kv_offsets"], b["max_q"], b["max_kv"],
-                                                    qk_scale=w.qk_scale, activation=w.activation)
-            o.backward(do)
-            host_out["o"].copy_(o.detach(), non_blocking=True)
-            host_out["dq"].copy_(q.grad, non_blocking=True)
-            host_out["dk"].copy_(k.grad, non_blocking=True)
-            host_out["dv"].copy_(v.grad, non_blocking=True)
+            # public host-buffer entry point: token-balanced chunks, copies overlapped with the kernels
+            G.forward_backward_host(host_in["q"], host_in["k"], host_in["v"], host_in["do"], host_off["q"], host_off["k"],
+                                    qk_scale=w.qk_scale, activation=w.activation, out=host_out, n_chunks=args.e2e_chunks,
+                                    device=dev)
 
         e2e_step()
         barrier()
@@ -353,7 +349,8 @@ def main():
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = float(te.item()) / args.e2e_steps
         e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
-               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps}
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+               "api": "gdpa.forward_backward_host (pinned host Q, K, V, dO in; O, dQ, dK, dV out; %d chunks, copies overlapped with compute)" % args.e2e_chunks}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -220,6 +220,12 @@ const char* gdpa_strerror(int code);
  * Used by benchmarks to report how many of this library's kernels ran in a timed region. */
 int64_t gdpa_launch_count(void);
 
+/* Diagnostic: launch a one-warp kernel whose single wait can never be satisfied and gives up after
+ * `limit_ns` nanoseconds (at most 1 s): it must write a non-zero code to *status (device int32) and
+ * return normally, leaving the context usable.  This is the give-up path of every in-kernel wait of
+ * the library, exercised without hanging or faulting the GPU. */
+int gdpa_debug_wait_probe(int32_t* status, uint64_t limit_ns, gdpa_stream_t stream);
+
 /* Diagnostic hook for performance analysis: register a device buffer of 16384 int64 slots into which
  * CTA 0 of the forward / backward kernels writes SM cycle stamps at fixed points of its pipeline
  * (slot layout in csrc/gdpa_fwd.cu and csrc/gdpa_bwd.cu), or null to switch tracing off (default).

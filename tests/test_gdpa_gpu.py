@@ -172,3 +172,38 @@ def test_host_errors_are_raised_before_any_launch(G):
         G.generalized_dot_product_attention(q96, k96, k96, dev["qo"], dev["ko"], 10, 12)
     with pytest.raises(ValueError):
         G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"][:1], 10, 12)
+
+
+def test_bounded_wait_gives_up_and_reports_without_hanging(G):
+    """A wait nothing satisfies runs out after its limit, writes a status code and returns; the
+    context stays usable (the next operator call works)."""
+    import ctypes as C
+
+    from ads_model_kernel_library_b200.gdpa import _cabi
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = _cabi.lib.gdpa_debug_wait_probe(C.c_void_p(status.data_ptr()), 20_000_000,  # 20 ms
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == (0x7700 | 1)
+    assert _cabi.lib.gdpa_debug_wait_probe(None, 1000, None) == 1  # bad arguments are refused on the host
+    cpu, dev = jagged_inputs([100], [100], 1, 64, seed=2, std=0.5)
+    o = run_fwd(G, dev, [100], [100], "relu", 0.1)
+    assert_close(o, oracle_forward(cpu, "relu", 0.1), "O after a timed-out probe")
+
+
+def test_host_buffer_pipeline_matches_direct_call(G):
+    """forward_backward_host (pinned host tensors, chunked, copies overlapped) == one direct call."""
+    rng = np.random.default_rng(4)
+    lq, lk = rng.integers(1, 400, 23), rng.integers(1, 500, 23)
+    cpu, dev = jagged_inputs(lq, lk, 2, 128, seed=13, std=0.5)
+    o, dq, dk, dv = run_fwd_bwd(G, dev, lq, lk, "gelu_approx", 1.0 / 64)
+    pinned = {n: cpu[n].pin_memory() for n in ("q", "k", "v", "do")}
+    res = G.forward_backward_host(pinned["q"], pinned["k"], pinned["v"], pinned["do"], cpu["qo"], cpu["ko"],
+                                  qk_scale=1.0 / 64, activation="gelu_approx", n_chunks=5)
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    assert torch.equal(res["o"], o.cpu())
+    assert torch.equal(res["dk"], dk.cpu()) and torch.equal(res["dv"], dv.cpu())
+    assert_close(res["dq"], dq.float(), "dQ (host pipeline)", atol=1e-2, rtol=1e-2)
