@@ -52,8 +52,9 @@ enum FwdBar : int {
   B_P_FULL = 6 + 2 * kKvStages,        // [2] activation group (128 arrivals) -> MMA
   B_O_FULL = 8 + 2 * kKvStages,        // [2] MMA commit -> epilogue
   B_O_EMPTY = 10 + 2 * kKvStages,      // [2] epilogue (128 arrivals) -> MMA
-  B_L_FULL = 12 + 2 * kKvStages,       // [2] softmax: activation group (128 arrivals) -> epilogue (row sums)
-  B_COUNT = 14 + 2 * kKvStages
+  B_L_FULL = 12 + 2 * kKvStages,       // [2] softmax: activation group -> epilogue (row sums)
+  B_M_FULL = 14 + 2 * kKvStages,       // [2] softmax, wide layout: both column halves have published their row maxima
+  B_COUNT = 16 + 2 * kKvStages
 };
 
 template <int D, int EB>
@@ -64,8 +65,9 @@ struct FwdSmem {
   static constexpr int kBoxCols = 128 / EB;              // elements per box row
   static constexpr int kQOff = 0;
   static constexpr int kKvOff = 2 * kTileBytes;
-  static constexpr int kRowSumOff = kKvOff + kKvStages * kTileBytes;  // softmax: float[2][128]
-  static constexpr int kBarOff = kRowSumOff + 2 * kTile * 4;
+  static constexpr int kRowSumOff = kKvOff + kKvStages * kTileBytes;  // softmax: float[2 Q tiles][2 halves][128]
+  static constexpr int kRowMaxOff = kRowSumOff + 4 * kTile * 4;       // softmax, wide: float[2 parity][2][2][128]
+  static constexpr int kBarOff = kRowMaxOff + 8 * kTile * 4;
   static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kBytes = kAbortOff + 4;
@@ -82,7 +84,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
-  static_assert(!(WIDE && (kSoftmax || FP8)), "the wide layout covers the element-wise bf16 activations");
   constexpr int kActWarps = WIDE ? 16 : 8;
   constexpr int kMmaWarp = WIDE ? 16 : 12;
   constexpr int kLoadWarp = WIDE ? 17 : 13;
@@ -104,7 +105,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool many = (i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2) ||
                         (i >= B_L_FULL && i < B_L_FULL + 2);
       uint32_t cnt = many ? 128u : 1u;
-      if ((i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2)) cnt = kStageThreads;
+      if ((i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2) ||
+          (i >= B_L_FULL && i < B_L_FULL + 2) || (i >= B_M_FULL && i < B_M_FULL + 2))
+        cnt = kStageThreads;
       mbar_init(bar_base + 8u * i, cnt);
     }
     *abort_flag = 0;
@@ -211,7 +214,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
           const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
           // wide layout: the P slices of column half h sit at the start of that half's own S columns
-          const uint32_t a_col = WIDE ? (kk >> 2) * 64 + (kk & 3) * 8 : kk * 8;
+          const uint32_t a_col = !WIDE ? kk * 8 : (FP8 ? (kk >> 1) * 64 + (kk & 1) * 8 : (kk >> 2) * 64 + (kk & 3) * 8);
           if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
           else umma_ts_f16(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
         }
@@ -305,7 +308,123 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         continue;
       }
-      for (int j = 0; j < nkv; ++j) {
+      float inv_l = 1.f;
+      if constexpr (kSoftmax) {
+        // ---- softmax, one row split over two warps (64 columns each): the halves publish their partial
+        // row maxima through shared memory and an mbarrier, take the common maximum, and keep partial row
+        // sums that the epilogue adds.  Otherwise as in the narrow layout.
+        constexpr float kThr = FP8 ? 1.f : 8.f;
+        constexpr float kPScale = FP8 ? 128.f : 1.f;
+        constexpr float kLog2e = 1.4426950408889634f;
+        float* rowmax = reinterpret_cast<float*>(smem + L::kRowMaxOff);
+        float* rowsum = reinterpret_cast<float*>(smem + L::kRowSumOff);
+        float m_used = -INFINITY, row_sum = 0.f;
+        float sq = 1.f;
+        long long kv_blk0 = 0;
+        if constexpr (FP8) {
+          sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
+          kv_blk0 = load_offset(a.kv_blk_off, w.b, a.off64);
+        }
+        for (int j = 0; j < nkv; ++j) {
+          const int valid = min(kTile, w.lkv - j * kTile) - half * 64;
+          float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
+          if constexpr (FP8) {
+            const float sk = a.k_scales[(kv_blk0 + j) * a.heads + w.h];
+            const float sv = a.v_scales[(kv_blk0 + j) * a.heads + w.h];
+            c *= sq * sk;
+            bias = log2f(sv);
+            inv_sv = 1.f / sv;
+          }
+          GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+          tc_fence_after();
+          uint32_t ra[32], rb[32];
+          // pass 1: partial row maximum of c * S over this warp's valid columns (chunk 1 in flight
+          // while chunk 0 is scanned)
+          float pmax = -INFINITY;
+          tmem_ld32(s_tmem, ra);
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t(&cur)[32] = ch ? rb : ra;
+            tmem_wait_ld();
+            tmem_regs_ready(cur);
+            if (ch == 0) tmem_ld32(s_tmem + 32, rb);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float t = __uint_as_float(cur[i]) * c;
+              pmax = (ch * 32 + i < valid) ? fmaxf(pmax, t) : pmax;
+            }
+          }
+          float* slot = rowmax + (((s_phase * 2 + s) * 2) * kTile);
+          slot[half * kTile + row] = pmax;
+          mbar_arrive(bar_base + 8u * (B_M_FULL + s));
+          GDPA_WAIT(B_M_FULL + s, s_phase, ST_ROLE_ACT);
+          const float rmax = fmaxf(pmax, reinterpret_cast<volatile float*>(slot)[(half ^ 1) * kTile + row]);
+          s_phase ^= 1u;
+          const float m_new = fmaxf(m_used, rmax + bias);
+          if (j == 0) {
+            m_used = m_new;
+          } else if (__any_sync(0xffffffffu, m_new > m_used + kThr)) {
+            const float alpha = ex2_approx(m_used - m_new);
+            row_sum *= alpha;
+            m_used = m_new;
+#pragma unroll
+            for (int ch = 0; ch < D / 64; ++ch) {
+              uint32_t ro[32];
+              tmem_ld32(o_tmem + ch * 32, ro);
+              tmem_wait_ld();
+              tmem_regs_ready(ro);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+              tmem_st32(o_tmem + ch * 32, ro);
+            }
+          }
+          // pass 2: reload the scores, P = exp2(c S + bias - m), partial row sum, quantise, store over
+          // columns of this half that have been read
+          const float off = bias - m_used;
+          float psum = 0.f;
+          tmem_ld32(s_tmem, ra);
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t(&cur)[32] = ch ? rb : ra;
+            tmem_wait_ld();
+            tmem_regs_ready(cur);
+            if (ch == 0) tmem_ld32(s_tmem + 32, rb);
+            auto prob = [&](int i) {
+              const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
+              const float p = (ch * 32 + i < valid) ? e : 0.f;
+              psum += p;
+              return p;
+            };
+            if constexpr (FP8) {
+              uint32_t pk[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float p0 = prob(4 * i), p1 = prob(4 * i + 1), p2 = prob(4 * i + 2), p3 = prob(4 * i + 3);
+                pk[i] = pack_e4m3x4(p0 * kPScale, p1 * kPScale, p2 * kPScale, p3 * kPScale);
+              }
+              tmem_st8(s_tmem + ch * 8, pk);
+            } else {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float p0 = prob(2 * i), p1 = prob(2 * i + 1);
+                pk[i] = pack_bf16x2(p0, p1);
+              }
+              tmem_st16(s_tmem + ch * 16, pk);
+            }
+          }
+          row_sum = fmaf(psum, inv_sv, row_sum);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_base + 8u * (B_P_FULL + s));
+        }
+        // both halves publish their partial row sums; each then divides its half of O by the total
+        rowsum[(s * 2 + half) * kTile + row] = row_sum * kPScale;
+        mbar_arrive(bar_base + 8u * (B_L_FULL + s));
+        GDPA_WAIT(B_L_FULL + s, o_phase, ST_ROLE_EPI);
+        inv_l = 1.f / (row_sum * kPScale + reinterpret_cast<volatile float*>(rowsum)[(s * 2 + (half ^ 1)) * kTile + row]);
+      }
+      for (int j = 0; !kSoftmax && j < nkv; ++j) {
         const int valid = min(kTile, w.lkv - j * kTile) - half * 64;  // valid columns among this warp's 64
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
         GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
@@ -360,10 +479,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv_l, __uint_as_float(r[8 * i + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv_l, __uint_as_float(r[8 * i + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv_l, __uint_as_float(r[8 * i + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv_l, __uint_as_float(r[8 * i + 7]) * inv_l);
             dst[c * 4 + i] = v;
           }
         }
@@ -487,7 +606,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mbar_arrive(bar_base + 8u * (B_P_FULL + s));
         }
         // hand the row sum to the epilogue (it divides O by it)
-        reinterpret_cast<float*>(smem + L::kRowSumOff)[s * kTile + (warp & 3) * 32 + lane] = row_sum * kPScale;
+        reinterpret_cast<float*>(smem + L::kRowSumOff)[s * 2 * kTile + (warp & 3) * 32 + lane] = row_sum * kPScale;
         mbar_arrive(bar_base + 8u * (B_L_FULL + s));
         continue;
       }
@@ -559,7 +678,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float inv_l = 1.f;
         if constexpr (kSoftmax) {
           GDPA_WAIT(B_L_FULL + s, o_phase[s], ST_ROLE_EPI);
-          inv_l = 1.f / reinterpret_cast<volatile float*>(smem + L::kRowSumOff)[s * kTile + row];
+          inv_l = 1.f / reinterpret_cast<volatile float*>(smem + L::kRowSumOff)[s * 2 * kTile + row];
         }
         o_phase[s] ^= 1u;
         tc_fence_after();
@@ -610,7 +729,7 @@ role_done:
 template <int D, int ACT, bool FP8>
 int launch_fwd_inst(const FwdLaunch& l) {
   using L = FwdSmem<D, FP8 ? 1 : 2>;
-  constexpr bool kWide = !FP8 && ACT != ACT_SOFTMAX;
+  constexpr bool kWide = true;  // the narrow layout (kWide = false) remains instantiable for comparison
   auto kernel = gdpa_fwd_kernel<D, ACT, FP8, kWide>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;

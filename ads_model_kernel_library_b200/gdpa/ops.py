@@ -440,3 +440,37 @@ def generalized_dot_product_attention_fp8(
         q_block_offsets, kv_block_offsets, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale,
         act_id,
     )
+
+
+def _valid_pairs(query_offset: torch.Tensor, key_offset: torch.Tensor, max_q: int, max_kv: int) -> int:
+    """sum over sequences of Lq * Lkv (lengths clamped like the kernels clamp them).  Reads the offsets
+    on the host when they are real tensors; for meta / fake tensors falls back to batch * max_q * max_kv."""
+    batch = query_offset.shape[0] - 1
+    if query_offset.is_meta or key_offset.is_meta or type(query_offset).__name__ == "FakeTensor":
+        return batch * int(max_q) * int(max_kv)
+    qo = query_offset.detach().to("cpu", torch.int64)
+    ko = key_offset.detach().to("cpu", torch.int64)
+    lq = (qo[1:] - qo[:-1]).clamp(0, int(max_q))
+    lk = (ko[1:] - ko[:-1]).clamp(0, int(max_kv))
+    return int((lq * lk).sum())
+
+
+def _register_flop_formulas() -> None:
+    """Let torch.utils.flop_counter.FlopCounterMode see the operator, as the reference does
+    (gdpa/triton/triton_generalized_dot_product_attention.py:4051, :4137): 4 H D sum(Lq Lkv) forward,
+    2.5x that backward, valid jagged pairs only."""
+    try:
+        from torch.utils.flop_counter import register_flop_formula
+    except ImportError:  # pragma: no cover
+        return
+
+    @register_flop_formula(torch.ops.gdpa.generalized_dot_product_attention, get_raw=True)
+    def _fwd_flops(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, *args, **kwargs) -> int:
+        return 4 * query.shape[1] * query.shape[2] * _valid_pairs(query_offset, key_offset, max_seq_len_q, max_seq_len_kv)
+
+    @register_flop_formula(torch.ops.gdpa.generalized_dot_product_attention_backward, get_raw=True)
+    def _bwd_flops(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, *args, **kwargs) -> int:
+        return 10 * query.shape[1] * query.shape[2] * _valid_pairs(query_offset, key_offset, max_seq_len_q, max_seq_len_kv)
+
+
+_register_flop_formulas()

@@ -207,3 +207,48 @@ def test_host_buffer_pipeline_matches_direct_call(G):
     assert torch.equal(res["o"], o.cpu())
     assert torch.equal(res["dk"], dk.cpu()) and torch.equal(res["dv"], dv.cpu())
     assert_close(res["dq"], dq.float(), "dQ (host pipeline)", atol=1e-2, rtol=1e-2)
+
+
+def test_flop_counter_mode_sees_the_operator(G):
+    from torch.utils.flop_counter import FlopCounterMode
+
+    lq, lk = [100, 37], [64, 200]
+    cpu, dev = jagged_inputs(lq, lk, 2, 64, seed=3, std=0.5)
+    q = dev["q"].clone().requires_grad_(True)
+    with FlopCounterMode(display=False) as fc:
+        o = G.generalized_dot_product_attention(q, dev["k"], dev["v"], dev["qo"], dev["ko"], 100, 200, activation="relu")
+        o.backward(dev["do"])
+    pairs = 100 * 64 + 37 * 200
+    assert fc.get_total_flops() == 14 * 2 * 64 * pairs
+
+
+def test_reduced_zipf_config5_shapes(G):
+    """Heavily skewed lengths (32 * min(Zipf(1.2), 256), H=4, D=128, GELU-tanh): a reduced batch of the
+    sharded configuration against the oracle, plus the two-shard split of it against the unsharded run."""
+    from ads_model_kernel_library_b200.gdpa.sharding import shard_inputs
+
+    rng = np.random.default_rng(5)
+    ln = (32 * np.minimum(rng.zipf(1.2, 40), 256)).astype(np.int64)
+    ln = np.minimum(ln, 2048)  # keep the CPU oracle in seconds
+    cpu, dev = jagged_inputs(ln, ln, 4, 128, seed=55, std=0.5)
+    scale = 1.0 / int(ln.max())
+    o, dq, dk, dv = run_fwd_bwd(G, dev, ln, ln, "gelu_approx", scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "gelu_approx", scale)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+    # token-balanced split in two: each shard alone reproduces its rows of the unsharded output bit for bit
+    for rank in range(2):
+        q_r, k_r, v_r, qo_r, ko_r, (s, e), (r0, r1) = shard_inputs(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], rank, 2)
+        o_r = G.generalized_dot_product_attention(q_r.contiguous(), k_r.contiguous(), v_r.contiguous(), qo_r, ko_r,
+                                                  int(ln[s:e].max()), int(ln[s:e].max()), qk_scale=scale,
+                                                  activation="gelu_approx")
+        assert torch.equal(o_r, o[r0:r1])
+
+
+def test_many_heads_and_int32_offsets_backward(G):
+    lq, lk = [150, 31, 260], [90, 300, 129]
+    cpu, dev = jagged_inputs(lq, lk, 16, 64, seed=77, std=0.5, offset_dtype=torch.int32)
+    o, dq, dk, dv = run_fwd_bwd(G, dev, lq, lk, "silu", 1.0 / 32)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "silu", 1.0 / 32)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)

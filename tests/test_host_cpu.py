@@ -140,3 +140,13 @@ def test_workload_generators_are_seeded_and_shaped():
     c5 = make_workload("c5_zipf_sharded")
     assert c5.q_lens.min() >= 32 and c5.q_lens.max() == 8192 and len(c5.q_lens) == 8192
     assert useful_flops([2], [3], 1, 64, "bwd") == 10 * 64 * 6
+
+
+def test_flop_formula_counts_valid_pairs_only():
+    from ads_model_kernel_library_b200.gdpa import ops
+
+    qo, ko = torch.tensor([0, 3, 10]), torch.tensor([0, 5, 9])
+    assert ops._valid_pairs(qo, ko, 100, 100) == 3 * 5 + 7 * 4
+    assert ops._valid_pairs(qo, ko, 4, 100) == 3 * 5 + 4 * 4  # clamped to max_seq_len_q
+    meta = torch.empty(3, device="meta", dtype=torch.int64)
+    assert ops._valid_pairs(meta, meta, 8, 16) == 2 * 8 * 16
