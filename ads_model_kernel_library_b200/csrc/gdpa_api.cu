@@ -216,6 +216,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.sched = static_cast<const int*>(p->schedule);
   l.args.status = p->status;
   l.args.trace = g_trace.load();
+  l.args.lse = (!fp8 && act == ACT_SOFTMAX) ? p->lse : nullptr;
+  l.args.total_q = p->total_q;
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -245,7 +247,8 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   if (rc != GDPA_OK) return rc;
   if (p->dtype != GDPA_DTYPE_BF16) return GDPA_ERR_UNSUPPORTED_DTYPE;
   const int act = act_class_from_id(p->activation);
-  if (act < 0 || act == ACT_SOFTMAX) return GDPA_ERR_UNSUPPORTED_ACT;
+  if (act < 0) return GDPA_ERR_UNSUPPORTED_ACT;
+  if (act == ACT_SOFTMAX && (p->o == nullptr || p->lse == nullptr || p->dpsum == nullptr)) return GDPA_ERR_BAD_ARG;
   if (p->batch == 0 || (p->total_q == 0 && p->total_kv == 0)) return GDPA_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t elems_q = static_cast<size_t>(p->total_q) * p->heads * p->head_dim;
@@ -294,9 +297,18 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.sched = static_cast<const int*>(p->schedule);
   l.args.status = p->status;
   l.args.trace = g_trace.load();
+  l.args.lse = p->lse;
+  l.args.dpsum = p->dpsum;
+  l.args.total_q = p->total_q;
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+  if (act == ACT_SOFTMAX) {
+    rc = launch_dpsum(static_cast<const __nv_bfloat16*>(p->d_o), static_cast<const __nv_bfloat16*>(p->o), p->dpsum,
+                      p->total_q, p->heads, p->head_dim, st);
+    if (rc != 0) return rc;
+    g_launches.fetch_add(1);
+  }
   if (p->timing_start_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_start_event), st);
   rc = launch_bwd_bf16(l, p->head_dim, act);
   if (p->timing_stop_event != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(p->timing_stop_event), st);

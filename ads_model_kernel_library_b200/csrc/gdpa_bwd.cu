@@ -58,7 +58,8 @@ enum BwdBar : int {
   BB_DQ_EMPTY = 15, // 128 arrivals
   BB_DKV_FULL = 16,
   BB_DKV_EMPTY = 17,// 256 arrivals
-  BB_COUNT = 18
+  BB_ST_FULL = 18,  // 256 arrivals: softmax, the per-column statistics of a Q tile are in shared memory
+  BB_COUNT = 19
 };
 
 template <int D>
@@ -76,7 +77,8 @@ struct BwdSmem {
   static constexpr int kBarOff = kDqOff + 2 * kDqSlabBytes;
   static constexpr int kTmemPtrOff = kBarOff + BB_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
-  static constexpr int kBytes = kAbortOff + 4;
+  static constexpr int kStatOff = (kAbortOff + 4 + 15) / 16 * 16;  // softmax: float lse[128], dpsum[2][128]
+  static constexpr int kBytes = kStatOff + 3 * kTile * 4;
   static constexpr int kDynBytes = kBytes + 1024;
 };
 
@@ -115,7 +117,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < BB_COUNT; ++i) {
       uint32_t cnt = 1;
-      if (i == BB_P_FULL || i == BB_DS_FULL || i == BB_DKV_EMPTY) cnt = 256;
+      if (i == BB_P_FULL || i == BB_DS_FULL || i == BB_DKV_EMPTY || i == BB_ST_FULL) cnt = 256;
       if (i == BB_DQ_EMPTY) cnt = 128;
       mbar_init(bar_base + 8u * i, cnt);
     }
@@ -313,9 +315,14 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tS = tmem_base + lane_base + kColS, tDP = tmem_base + lane_base + kColDP;
     const float scale = a.scale, hscale = 0.5f * a.scale;
     uint8_t* sds_row = smem + L::kDsOff + half * L::kHalfBytes + row * 128;
-    uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0;
+    uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0, st_phase = 0;
     int tr = 0;
     const bool tracer = (threadIdx.x == 128);
+    constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
+    float* stat_lse = reinterpret_cast<float*>(smem + L::kStatOff);
+    float* stat_dps = stat_lse + kTile;  // two buffers, by parity of the Q tile
+    const int ew_tid = threadIdx.x - 128;  // 0..255 among the element-wise threads
+    const float c2 = a.scale * 1.4426950408889634f;
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
@@ -342,10 +349,28 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
         uint32_t ra[32], rb[32];
         if (tracer) GDPA_TRACE(a, tr * 32 + 8);
+        float stat = 0.f;
+        if constexpr (kSoftmax) {
+          // this thread's share of the Q tile's column statistics: lse for threads 0-127, dPsum for 128-255
+          const int qc = m * kTile + (ew_tid & 127);
+          if (qc < w.lq) {
+            const long long at = static_cast<long long>(w.h) * a.total_q + w.q_start + qc;
+            stat = (ew_tid < 128) ? a.lse[at] : a.dpsum[at];
+          }
+        }
         GDPA_WAIT(BB_S_FULL, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
         if (tracer) GDPA_TRACE(a, tr * 32 + 9);
+        if constexpr (kSoftmax) {
+          // S(m) ready means every thread has left phase 1 of tile m-1 (lse buffer free) and phase 2 of tile
+          // m-2 (dPsum buffer of this parity free)
+          if (ew_tid < 128) stat_lse[ew_tid] = stat;
+          else stat_dps[(m & 1) * kTile + (ew_tid - 128)] = stat;
+          mbar_arrive(bar_base + 8u * BB_ST_FULL);
+          GDPA_WAIT(BB_ST_FULL, st_phase, ST_ROLE_ACT);
+          st_phase ^= 1u;
+        }
         tmem_ld32(tS + half * 64, ra);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -354,7 +379,20 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_wait_ld();
           tmem_regs_ready(cur);
           if (c == 0) tmem_ld32(tS + half * 64 + 32, rb);
-          if (full) {
+          if constexpr (kSoftmax) {
+            // P^T = 2^(c S^T - lse[q]) (already normalised); kept in g2 for dS = scale P (dP - dPsum)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = half * 64 + c * 32 + 2 * i;
+              const float2 l2 = *reinterpret_cast<const float2*>(stat_lse + col);
+              float p0 = ex2_approx(fmaf(__uint_as_float(cur[2 * i]), c2, -l2.x));
+              float p1 = ex2_approx(fmaf(__uint_as_float(cur[2 * i + 1]), c2, -l2.y));
+              p0 = (row_valid && col < qv) ? p0 : 0.f;
+              p1 = (row_valid && col + 1 < qv) ? p1 : 0.f;
+              pk[i] = pack_bf16x2(p0, p1);
+              g2[c * 16 + i] = pack_f32x2(p0, p1);
+            }
+          } else if (full) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               act_and_grad_pair<ACT, false>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
@@ -393,9 +431,17 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               float d0, d1;
-              unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e],
-                                     pack_f32x2(__uint_as_float(cur[8 * j + 2 * e]), __uint_as_float(cur[8 * j + 2 * e + 1]))),
-                           d0, d1);
+              if constexpr (kSoftmax) {
+                const float2 ps = *reinterpret_cast<const float2*>(stat_dps + (m & 1) * kTile + half * 64 + c * 32 + 8 * j + 2 * e);
+                float p0, p1;
+                unpack_f32x2(g2[c * 16 + 4 * j + e], p0, p1);
+                d0 = p0 * (__uint_as_float(cur[8 * j + 2 * e]) - ps.x) * scale;
+                d1 = p1 * (__uint_as_float(cur[8 * j + 2 * e + 1]) - ps.y) * scale;
+              } else {
+                unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e],
+                                       pack_f32x2(__uint_as_float(cur[8 * j + 2 * e]), __uint_as_float(cur[8 * j + 2 * e + 1]))),
+                             d0, d1);
+              }
               d[e] = pack_bf16x2(d0, d1);
             }
             // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
@@ -544,6 +590,26 @@ __global__ void __launch_bounds__(256) gdpa_dq_convert_kernel(const float4* __re
   }
 }
 
+// dPsum[h, t] = sum_d dO[t, h, d] * O[t, h, d] (fp32), one warp per (token, head) row.
+__global__ void __launch_bounds__(256) gdpa_dpsum_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
+                                                         float* __restrict__ dpsum, long long total_q, int heads, int head_dim) {
+  const long long rows = total_q * heads;
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(d_o + r * head_dim);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(o + r * head_dim);
+    float acc = 0.f;
+    for (int i = lane; i < head_dim / 2; i += 32) {
+      const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(b2[i]);
+      acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (lane == 0) dpsum[(r % heads) * total_q + r / heads] = acc;
+  }
+}
+
 template <int D, int ACT>
 int launch_bwd_inst(const BwdLaunch& l) {
   using L = BwdSmem<D>;
@@ -565,6 +631,7 @@ int launch_bwd_d(const BwdLaunch& l, int act_class) {
     case ACT_SILU: return launch_bwd_inst<D, ACT_SILU>(l);
     case ACT_HARDSWISH: return launch_bwd_inst<D, ACT_HARDSWISH>(l);
     case ACT_RELU_SQUARE: return launch_bwd_inst<D, ACT_RELU_SQUARE>(l);
+    case ACT_SOFTMAX: return launch_bwd_inst<D, ACT_SOFTMAX>(l);
     default: return GDPA_ERR_UNSUPPORTED_ACT_;
   }
 }
@@ -575,6 +642,16 @@ int launch_bwd_bf16(const BwdLaunch& l, int head_dim, int act_class) {
   if (head_dim == 128) return launch_bwd_d<128>(l, act_class);
   if (head_dim == 64) return launch_bwd_d<64>(l, act_class);
   return GDPA_ERR_UNSUPPORTED_DIM_;
+}
+
+int launch_dpsum(const __nv_bfloat16* d_o, const __nv_bfloat16* o, float* dpsum, long long total_q, int heads, int head_dim,
+                 cudaStream_t stream) {
+  const long long rows = total_q * heads;
+  if (rows == 0) return 0;
+  long long blocks = (rows + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  gdpa_dpsum_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(d_o, o, dpsum, total_q, heads, head_dim);
+  return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 
 int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {

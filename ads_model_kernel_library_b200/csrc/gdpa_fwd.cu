@@ -423,6 +423,11 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive(bar_base + 8u * (B_L_FULL + s));
         GDPA_WAIT(B_L_FULL + s, o_phase, ST_ROLE_EPI);
         inv_l = 1.f / (row_sum * kPScale + reinterpret_cast<volatile float*>(rowsum)[(s * 2 + (half ^ 1)) * kTile + row]);
+        if constexpr (!FP8) {
+          // log-sum-exp of the scaled scores in base 2, for the softmax backward
+          if (half == 0 && row_valid && a.lse != nullptr)
+            a.lse[static_cast<long long>(w.h) * a.total_q + w.q_start + qr] = m_used - log2f(inv_l);
+        }
       }
       for (int j = 0; !kSoftmax && j < nkv; ++j) {
         const int valid = min(kTile, w.lkv - j * kTile) - half * 64;  // valid columns among this warp's 64

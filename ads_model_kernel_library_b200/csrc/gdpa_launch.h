@@ -32,6 +32,8 @@ struct FwdArgs {
   const void* q_blk_off;
   const void* kv_blk_off;
   long long* trace;  // optional cycle-stamp buffer of CTA 0 (performance analysis); null in normal use
+  float* lse;        // softmax: optional [heads, total_q] log-sum-exp output (base 2)
+  long long total_q;
 };
 
 struct FwdLaunch {
@@ -55,6 +57,9 @@ struct BwdArgs {
   const int* sched;
   int* status;
   long long* trace;  // optional cycle-stamp buffer of CTA 0; null in normal use
+  const float* lse;    // softmax backward: [heads, total_q] log-sum-exp of the forward (base 2)
+  const float* dpsum;  // softmax backward: [heads, total_q] rowsum(dO * O)
+  long long total_q;
 };
 
 struct BwdLaunch {
@@ -81,6 +86,8 @@ int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class);
 int launch_fwd_softmax_bf16(const FwdLaunch& l, int head_dim);
 int launch_fwd_fp8(const FwdLaunch& l, int head_dim, int act_class);
 int launch_bwd_bf16(const BwdLaunch& l, int head_dim, int act_class);
+int launch_dpsum(const __nv_bfloat16* d_o, const __nv_bfloat16* o, float* dpsum, long long total_q, int heads, int head_dim,
+                 cudaStream_t stream);
 int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
 

@@ -81,6 +81,7 @@ class GdpaFwdParams(C.Structure):
         ("kv_block_offsets", C.c_void_p),
         ("timing_start_event", C.c_void_p),
         ("timing_stop_event", C.c_void_p),
+        ("lse", C.c_void_p),
     ]
 
 
@@ -112,6 +113,9 @@ class GdpaBwdParams(C.Structure):
         ("status", C.c_void_p),
         ("timing_start_event", C.c_void_p),
         ("timing_stop_event", C.c_void_p),
+        ("o", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("dpsum", C.c_void_p),
     ]
 
 

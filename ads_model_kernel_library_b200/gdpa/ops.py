@@ -188,10 +188,12 @@ def _gdpa_backward_op(
     max_seq_len_kv: int,
     qk_scale: float,
     activation: int,
+    out: Optional[torch.Tensor] = None,
+    lse: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
-    if activation == SOFTMAX_ID:
-        raise NotImplementedError("the softmax activation has no backward in this library")
+    if activation == SOFTMAX_ID and (out is None or lse is None):
+        raise ValueError("the softmax backward needs the forward output and its log-sum-exp")
     if do.shape != query.shape or do.dtype != query.dtype:
         raise ValueError("grad_output must have the shape and dtype of query")
     do = do.contiguous()
@@ -221,13 +223,18 @@ def _gdpa_backward_op(
         p.schedule = sched.data_ptr()
         p.dq_accum = dq_accum.data_ptr()
         p.status = _status_word(query.device).data_ptr()
+        if activation == SOFTMAX_ID:
+            dpsum = torch.empty(max(query.shape[0] * H, 1), dtype=torch.float32, device=query.device)
+            out = out.contiguous()
+            p.o, p.lse, p.dpsum = out.data_ptr(), lse.data_ptr(), dpsum.data_ptr()
         _set_timing(p, "bwd")
         _cabi.check(_cabi.lib.gdpa_bwd(C.byref(p), _stream_ptr()), "gdpa_bwd")
     return dq, dk, dv
 
 
 @_gdpa_backward_op.register_fake
-def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, out=None,
+      lse=None):
     return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
 
 
@@ -246,6 +253,57 @@ def _backward(ctx, do):
 
 
 _gdpa_forward_op.register_autograd(_backward, setup_context=_setup_context)
+
+
+@torch.library.custom_op("gdpa::generalized_dot_product_attention_softmax", mutates_args=(), device_types="cuda")
+def _gdpa_forward_softmax_op(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: float,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax forward that also returns the base-2 log-sum-exp ``[H, total_q]`` its backward needs."""
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    with torch.cuda.device(query.device):
+        o = torch.empty_like(query)
+        lse = torch.zeros((H, query.shape[0]), dtype=torch.float32, device=query.device)
+        if query.shape[0] == 0 or batch == 0:
+            return o, lse
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
+                                max_seq_len_q, max_seq_len_kv)
+        p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
+                             max_seq_len_kv, qk_scale, SOFTMAX_ID, sched, _cabi.GDPA_DTYPE_BF16)
+        p.lse = lse.data_ptr()
+        _set_timing(p, "fwd")
+        _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
+    return o, lse
+
+
+@_gdpa_forward_softmax_op.register_fake
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale):
+    return torch.empty_like(query), torch.empty((query.shape[1], query.shape[0]), dtype=torch.float32, device=query.device)
+
+
+def _softmax_setup_context(ctx, inputs, output):
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale = inputs
+    o, lse = output
+    ctx.save_for_backward(query, key, value, query_offset, key_offset, o, lse)
+    ctx.max_q, ctx.max_kv, ctx.qk_scale = max_q, max_kv, qk_scale
+
+
+def _softmax_backward(ctx, do, dlse):
+    query, key, value, query_offset, key_offset, o, lse = ctx.saved_tensors
+    dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
+        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, SOFTMAX_ID, o, lse
+    )
+    return dq, dk, dv, None, None, None, None, None
+
+
+_gdpa_forward_softmax_op.register_autograd(_softmax_backward, setup_context=_softmax_setup_context)
 
 
 @torch.library.custom_op("gdpa::generalized_dot_product_attention_fp8", mutates_args=(), device_types="cuda")
@@ -342,8 +400,8 @@ def generalized_dot_product_attention(
     Same signature as the reference entry point.  ``query`` is ``[total_q, H, D]``, ``key`` and
     ``value`` are ``[total_kv, H, D]`` (bf16, D in {64, 128}); ``query_offset`` / ``key_offset`` are
     ``[B + 1]`` int32 or int64 prefix sums.  ``qk_scale=None`` means 1.0, as in the reference
-    (:3148-3149).  ``activation`` is a reference activation name, or ``"softmax"`` (forward only),
-    for which ``qk_scale`` multiplies the scores before the exponential.
+    (:3148-3149).  ``activation`` is a reference activation name, or ``"softmax"`` (forward and
+    backward), for which ``qk_scale`` multiplies the scores before the exponential.
 
     Scheduling knobs of the reference (``seq_index``, ``enable_persistent``, ``enable_tma``,
     ``enable_ws``, ``use_dq_atomic_add``, ``bwd_opt_tech``, ``allow_tf32``, ``total_num_objects``) are
@@ -379,6 +437,11 @@ def generalized_dot_product_attention(
     query = expect_contiguous(query)
     key = expect_contiguous(key)
     value = expect_contiguous(value)
+    if act_id == SOFTMAX_ID:
+        # the trainable softmax variant keeps the log-sum-exp of the forward for its backward
+        return torch.ops.gdpa.generalized_dot_product_attention_softmax(
+            query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale
+        )[0]
     return torch.ops.gdpa.generalized_dot_product_attention(
         query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id
     )

@@ -147,6 +147,10 @@ typedef struct GdpaFwdParams {
    * launch, so that a benchmark can time that kernel alone.  Null = not recorded. */
   void* timing_start_event;
   void* timing_stop_event;
+  /* Optional, GDPA_ACT_SOFTMAX with bf16 inputs only: fp32 [heads, total_q] log-sum-exp of the scaled
+   * scores in base 2 (log2 sum_kv 2^(qk_scale log2(e) S)), which gdpa_bwd needs for the softmax
+   * backward.  Null = not written. */
+  float* lse;
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
@@ -174,7 +178,8 @@ int gdpa_fwd_fp8(const GdpaFwdParams* params, gdpa_stream_t stream);
  * Backward.  Replaces torch.ops.gdpa.generalized_dot_product_attention_backward
  * (gdpa/triton/triton_generalized_dot_product_attention.py:3461-3788) and _flash_attn_bwd
  * (gdpa/src/interface.py:1257-1685): S and P are recomputed, dQ, dK, dV come out of one
- * persistent kernel; dQ is accumulated in fp32 (the reference reduces into bf16,
+ * persistent kernel (for GDPA_ACT_SOFTMAX: dS = qk_scale P (dP - dPsum), with P rebuilt from the
+ * forward's log-sum-exp); dQ is accumulated in fp32 (the reference reduces into bf16,
  * gdpa/src/flash_bwd_sm100.py:2267-2287) and rounded once by a second, bandwidth-bound kernel.
  * ------------------------------------------------------------------------------------------- */
 typedef struct GdpaBwdParams {
@@ -206,6 +211,13 @@ typedef struct GdpaBwdParams {
    * accumulator memset and the fp32 -> bf16 dQ rounding kernel).  Null = not recorded. */
   void* timing_start_event;
   void* timing_stop_event;
+  /* GDPA_ACT_SOFTMAX only (the softmax backward, which the reference leaves unimplemented:
+   * gdpa/src/flash_bwd_sm100.py:2038-2058 keeps the dPsum term commented out): the forward output O
+   * [total_q, heads, head_dim] bf16, the forward's lse [heads, total_q] fp32, and a scratch buffer of
+   * total_q * heads floats that receives dPsum = rowsum(dO * O). */
+  const void* o;
+  const float* lse;
+  float* dpsum;
 } GdpaBwdParams;
 
 /* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */
