@@ -171,6 +171,7 @@ int gdpa_build_schedule(const GdpaSchedParams* p, gdpa_stream_t stream) {
   a.mode = p->mode;
   a.sched = static_cast<int*>(p->schedule);
   a.capacity_items = (p->schedule_bytes - kSchedHeaderInts * 4) / 16;
+  a.kv_index = p->kv_seq_index;
   int rc = launch_build_schedule(a, static_cast<cudaStream_t>(stream));
   if (rc == 0) g_launches.fetch_add(1);
   return rc;
@@ -189,6 +190,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   if (fp8 && (p->q_scales == nullptr || p->k_scales == nullptr || p->v_scales == nullptr ||
               p->q_block_offsets == nullptr || p->kv_block_offsets == nullptr))
     return GDPA_ERR_BAD_ARG;
+  const int kv_heads = p->kv_heads > 0 ? p->kv_heads : p->heads;
+  if (p->heads % kv_heads != 0) return GDPA_ERR_BAD_ARG;
   DeviceInfo di;
   rc = device_info(&di);
   if (rc != GDPA_OK) return rc;
@@ -203,8 +206,9 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   const void* vp = p->total_kv > 0 ? p->v : p->q;
   const long long kv_rows = p->total_kv > 0 ? p->total_kv : p->total_q;
   if ((rc = make_tmap(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  const int kvh_map = p->total_kv > 0 ? kv_heads : p->heads;
+  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;
   l.args.kv_off = p->kv_offsets;
@@ -218,6 +222,9 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.trace = g_trace.load();
   l.args.lse = (!fp8 && act == ACT_SOFTMAX) ? p->lse : nullptr;
   l.args.total_q = p->total_q;
+  l.args.kv_heads = kv_heads;
+  l.args.kv_group = p->heads / kv_heads;
+  l.args.kv_index = p->kv_seq_index;
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -251,8 +258,10 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   if (act == ACT_SOFTMAX && (p->o == nullptr || p->lse == nullptr || p->dpsum == nullptr)) return GDPA_ERR_BAD_ARG;
   if (p->batch == 0 || (p->total_q == 0 && p->total_kv == 0)) return GDPA_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int kv_heads = p->kv_heads > 0 ? p->kv_heads : p->heads;
+  if (p->heads % kv_heads != 0) return GDPA_ERR_BAD_ARG;
   const size_t elems_q = static_cast<size_t>(p->total_q) * p->heads * p->head_dim;
-  const size_t elems_kv = static_cast<size_t>(p->total_kv) * p->heads * p->head_dim;
+  const size_t elems_kv = static_cast<size_t>(p->total_kv) * kv_heads * p->head_dim;
   if (p->total_q == 0) {
     // No query rows: dK = dV = 0.
     if (p->dk == nullptr || p->dv == nullptr) return GDPA_ERR_BAD_ARG;
@@ -277,8 +286,8 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   std::memset(&l, 0, sizeof(l));
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if ((rc = make_tmap(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
   if ((rc = make_tmap(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
   // fp32 dQ accumulator, reduced into by 32-column x 32-row boxes (128-byte swizzled staging).
   if ((rc = make_tmap(&l.tm_dq, p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
@@ -290,7 +299,9 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.q_off = p->q_offsets;
   l.args.kv_off = p->kv_offsets;
   l.args.off64 = p->offsets_are_int64;
-  l.args.heads = p->heads;
+  l.args.heads = kv_heads;
+  l.args.q_heads = p->heads;
+  l.args.kv_group = p->heads / kv_heads;
   l.args.max_q = p->max_seq_len_q;
   l.args.max_kv = p->max_seq_len_kv;
   l.args.scale = p->qk_scale;

@@ -159,7 +159,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int idx;
         while (walker.next(idx)) {
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-          const int nq = (w.lq + kTile - 1) / kTile;
+          const int nq1 = (w.lq + kTile - 1) / kTile;  // Q tiles of one query head
+          const int nq = nq1 * a.kv_group;             // ... of every query head of this K / V head's group
           if (nq == 0) continue;
           const int kv_row = static_cast<int>(w.kv_start) + w.blk * kTile;
           const int q_row = static_cast<int>(w.q_start);
@@ -176,6 +177,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v, bar, hf * 64, w.h, kv_row);
           }
           for (int m = 0; m < nq; ++m) {
+            const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
             GDPA_WAIT(BB_Q_EMPTY + st, q_phase[st] ^ 1u, ST_ROLE_LOAD);
             q_phase[st] ^= 1u;
             {
@@ -183,8 +185,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
               for (int hf = 0; hf < D / 64; ++hf)
-                tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, w.h,
-                            q_row + m * kTile);
+                tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, hq,
+                            q_row + mm * kTile);
             }
             GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
             do_phase ^= 1u;
@@ -193,7 +195,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
               for (int hf = 0; hf < D / 64; ++hf)
-                tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do, bar, hf * 64, w.h, q_row + m * kTile);
+                tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do, bar, hf * 64, hq, q_row + mm * kTile);
             }
             st ^= 1u;
           }
@@ -219,7 +221,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int idx;
         while (walker.next(idx)) {
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-          const int nq = (w.lq + kTile - 1) / kTile;
+          const int nq = ((w.lq + kTile - 1) / kTile) * a.kv_group;
           if (nq == 0) continue;
           GDPA_WAIT(BB_KV_FULL, kv_phase, ST_ROLE_MMA);
           kv_phase ^= 1u;
@@ -327,7 +329,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-      const int nq = (w.lq + kTile - 1) / kTile;
+      const int nq1 = (w.lq + kTile - 1) / kTile;
+      const int nq = nq1 * a.kv_group;
       const int kv_local = w.blk * kTile + row;
       const bool row_valid = kv_local < w.lkv;
       __nv_bfloat16* dk_row = a.dk + ((w.kv_start + kv_local) * a.heads + w.h) * static_cast<long long>(D);
@@ -344,7 +347,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       const bool tile_rows_full = (w.blk + 1) * kTile <= w.lkv;
       for (int m = 0; m < nq; ++m) {
-        const int qv = min(kTile, w.lq - m * kTile);  // valid Q columns of this tile
+        const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
+        const int qv = min(kTile, w.lq - mm * kTile);  // valid Q columns of this tile
         const bool full = tile_rows_full && qv == kTile;
         uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
         uint32_t ra[32], rb[32];
@@ -352,9 +356,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float stat = 0.f;
         if constexpr (kSoftmax) {
           // this thread's share of the Q tile's column statistics: lse for threads 0-127, dPsum for 128-255
-          const int qc = m * kTile + (ew_tid & 127);
+          const int qc = mm * kTile + (ew_tid & 127);
           if (qc < w.lq) {
-            const long long at = static_cast<long long>(w.h) * a.total_q + w.q_start + qc;
+            const long long at = static_cast<long long>(hq) * a.total_q + w.q_start + qc;
             stat = (ew_tid < 128) ? a.lse[at] : a.dpsum[at];
           }
         }
@@ -504,9 +508,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-      const int nq = (w.lq + kTile - 1) / kTile;
+      const int nq1 = (w.lq + kTile - 1) / kTile;
+      const int nq = nq1 * a.kv_group;
       for (int m = 0; m < nq; ++m) {
-        const int q_row0 = static_cast<int>(w.q_start) + m * kTile + warp * 32;
+        const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
+        const int q_row0 = static_cast<int>(w.q_start) + mm * kTile + warp * 32;
         uint32_t r[D / 32][32];
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 13);
         {
@@ -540,7 +546,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, w.h, q_row0);
+              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
               tma_store_commit();
             }
             ++slab;
@@ -548,9 +554,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         } else {
           // straight from registers: one 16-byte vector reduction per lane and 4 columns; rows beyond
           // the sequence are skipped (their values are zero anyway)
-          const int q_local = m * kTile + warp * 32 + lane;
+          const int q_local = mm * kTile + warp * 32 + lane;
           if (q_local < w.lq) {
-            float* dst = a.dq_accum + ((w.q_start + q_local) * a.heads + w.h) * static_cast<long long>(D);
+            float* dst = a.dq_accum + ((w.q_start + q_local) * a.q_heads + hq) * static_cast<long long>(D);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c)
 #pragma unroll

@@ -58,17 +58,21 @@ struct Work {
   int lq, lkv;
 };
 
+// `kv_index` (optional, same integer type as the offsets) maps a sequence to the entry of the KV offsets
+// it reads: the reference's ad_to_request_offset, where many Q sequences share one KV sequence
+// (gdpa/triton/triton_generalized_dot_product_attention.py:3961-3966).
 __device__ __forceinline__ Work load_work(const int* sched, int idx, const void* q_off, const void* kv_off, int is64,
-                                          int max_q, int max_kv) {
+                                          int max_q, int max_kv, const void* kv_index = nullptr) {
   const int4 it = reinterpret_cast<const int4*>(sched + kSchedHeaderInts)[idx];
   Work w;
   w.b = it.x;
   w.h = it.y;
   w.blk = it.z;
+  const int kb = kv_index != nullptr ? static_cast<int>(load_offset(kv_index, w.b, is64)) : w.b;
   w.q_start = load_offset(q_off, w.b, is64);
-  w.kv_start = load_offset(kv_off, w.b, is64);
+  w.kv_start = load_offset(kv_off, kb, is64);
   long long lq = load_offset(q_off, w.b + 1, is64) - w.q_start;
-  long long lkv = load_offset(kv_off, w.b + 1, is64) - w.kv_start;
+  long long lkv = load_offset(kv_off, kb + 1, is64) - w.kv_start;
   w.lq = static_cast<int>(lq < max_q ? lq : max_q);
   w.lkv = static_cast<int>(lkv < max_kv ? lkv : max_kv);
   if (w.lq < 0) w.lq = 0;

@@ -144,7 +144,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       WorkWalker walker(n_items);
       int idx;
       while (walker.next(idx)) {
-        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
         const int nkv = (w.lkv + kTile - 1) / kTile;
         if (nkv == 0) continue;
         const int q0 = w.blk * kFwdQBlock;
@@ -174,7 +174,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int hf = 0; hf < L::kBoxes; ++hf)
               tma_load_3d(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar,
-                          hf * L::kBoxCols, w.h, kv_row + j * kTile);
+                          hf * L::kBoxCols, w.h / a.kv_group, kv_row + j * kTile);
             if (++kv_stage == kKvStages) {
               kv_stage = 0;
               kv_phase ^= 1u;
@@ -222,7 +222,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       WorkWalker walker(n_items);
       int idx;
       while (walker.next(idx)) {
-        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+        const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
         const int nkv = (w.lkv + kTile - 1) / kTile;
         if (nkv == 0) continue;
         const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
@@ -293,7 +293,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
       const int nkv = (w.lkv + kTile - 1) / kTile;
       const int q0 = w.blk * kFwdQBlock;
       const int nst = (w.lq - q0 > kTile) ? 2 : 1;
@@ -323,14 +323,14 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         long long kv_blk0 = 0;
         if constexpr (FP8) {
           sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
-          kv_blk0 = load_offset(a.kv_blk_off, w.b, a.off64);
+          kv_blk0 = load_offset(a.kv_blk_off, a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, w.b, a.off64)) : w.b, a.off64);
         }
         for (int j = 0; j < nkv; ++j) {
           const int valid = min(kTile, w.lkv - j * kTile) - half * 64;
           float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
           if constexpr (FP8) {
-            const float sk = a.k_scales[(kv_blk0 + j) * a.heads + w.h];
-            const float sv = a.v_scales[(kv_blk0 + j) * a.heads + w.h];
+            const float sk = a.k_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
+            const float sv = a.v_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
             c *= sq * sk;
             bias = log2f(sv);
             inv_sv = 1.f / sv;
@@ -505,7 +505,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
       const int nkv = (w.lkv + kTile - 1) / kTile;
       const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
       if (nkv == 0 || s >= nst) continue;
@@ -522,15 +522,15 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         long long kv_blk0 = 0;
         if constexpr (FP8) {
           sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
-          kv_blk0 = load_offset(a.kv_blk_off, w.b, a.off64);
+          kv_blk0 = load_offset(a.kv_blk_off, a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, w.b, a.off64)) : w.b, a.off64);
         }
         const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
         for (int j = 0; j < nkv; ++j) {
           const int valid = min(kTile, w.lkv - j * kTile);
           float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
           if constexpr (FP8) {
-            const float sk = a.k_scales[(kv_blk0 + j) * a.heads + w.h];
-            const float sv = a.v_scales[(kv_blk0 + j) * a.heads + w.h];
+            const float sk = a.k_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
+            const float sv = a.v_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
             c *= sq * sk;
             bias = log2f(sv);
             inv_sv = 1.f / sv;
@@ -664,7 +664,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
       const int nkv = (w.lkv + kTile - 1) / kTile;
       const int q0 = w.blk * kFwdQBlock;
       const int nst = (w.lq - q0 > kTile) ? 2 : 1;

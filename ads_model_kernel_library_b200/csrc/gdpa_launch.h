@@ -34,6 +34,9 @@ struct FwdArgs {
   long long* trace;  // optional cycle-stamp buffer of CTA 0 (performance analysis); null in normal use
   float* lse;        // softmax: optional [heads, total_q] log-sum-exp output (base 2)
   long long total_q;
+  int kv_heads;      // K / V heads; query head h reads K / V head h / kv_group
+  int kv_group;      // heads / kv_heads
+  const void* kv_index;  // optional: sequence -> entry of the KV offsets (shared KV sequences)
 };
 
 struct FwdLaunch {
@@ -60,6 +63,8 @@ struct BwdArgs {
   const float* lse;    // softmax backward: [heads, total_q] log-sum-exp of the forward (base 2)
   const float* dpsum;  // softmax backward: [heads, total_q] rowsum(dO * O)
   long long total_q;
+  int q_heads;         // query heads; `heads` above is the number of K / V heads (the work items' heads)
+  int kv_group;        // q_heads / heads: a work item walks the Q tiles of every query head of its group
 };
 
 struct BwdLaunch {
@@ -80,6 +85,7 @@ struct SchedArgs {
   int mode;
   int* sched;
   long long capacity_items;
+  const void* kv_index;  // optional: sequence -> entry of the KV offsets
 };
 
 int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class);

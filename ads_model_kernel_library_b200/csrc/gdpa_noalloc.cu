@@ -79,6 +79,7 @@ extern "C" int gdpa_fwd_noalloc(const GdpaFwdParams* p, gdpa_stream_t stream) {
   sp.reserved = 0;
   sp.schedule = sched;
   sp.schedule_bytes = static_cast<int64_t>(sizeof(int)) * (kSchedHeaderInts + 4 * kNoallocMaxItems);
+  sp.kv_seq_index = p->kv_seq_index;
   if (p->batch > 0 && p->total_q > 0) {
     rc = gdpa_build_schedule(&sp, stream);
     if (rc != GDPA_OK) return rc;

@@ -49,6 +49,7 @@ class GdpaSchedParams(C.Structure):
         ("reserved", C.c_int32),
         ("schedule", C.c_void_p),
         ("schedule_bytes", C.c_int64),
+        ("kv_seq_index", C.c_void_p),
     ]
 
 
@@ -82,6 +83,9 @@ class GdpaFwdParams(C.Structure):
         ("timing_start_event", C.c_void_p),
         ("timing_stop_event", C.c_void_p),
         ("lse", C.c_void_p),
+        ("kv_heads", C.c_int32),
+        ("reserved0", C.c_int32),
+        ("kv_seq_index", C.c_void_p),
     ]
 
 
@@ -116,6 +120,8 @@ class GdpaBwdParams(C.Structure):
         ("o", C.c_void_p),
         ("lse", C.c_void_p),
         ("dpsum", C.c_void_p),
+        ("kv_heads", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

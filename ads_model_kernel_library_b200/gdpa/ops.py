@@ -77,7 +77,7 @@ def _stream_ptr() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check_inputs(q, k, v, qo, ko, dtype) -> Tuple[int, int, int]:
+def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False) -> Tuple[int, int, int]:
     for name, t in (("query", q), ("key", k), ("value", v)):
         if t.dim() != 3:
             raise ValueError(f"{name} must be [total_tokens, H, D], got {tuple(t.shape)}")
@@ -90,8 +90,10 @@ def _check_inputs(q, k, v, qo, ko, dtype) -> Tuple[int, int, int]:
     if k.shape != v.shape:
         raise ValueError("key and value must have the same shape")
     H, D = q.shape[1], q.shape[2]
-    if k.shape[1] != H or k.shape[2] != D:
-        raise NotImplementedError("query and key/value must have the same number of heads and head_dim")
+    if k.shape[2] != D:
+        raise NotImplementedError("query and key/value must have the same head_dim")
+    if k.shape[1] < 1 or H % k.shape[1] != 0:
+        raise ValueError("the number of query heads must be a multiple of the number of key/value heads")
     if D not in _SUPPORTED_HEAD_DIMS:
         raise NotImplementedError(f"head_dim {D} is not supported (supported: {_SUPPORTED_HEAD_DIMS})")
     for name, t in (("query_offset", qo), ("key_offset", ko)):
@@ -103,12 +105,13 @@ def _check_inputs(q, k, v, qo, ko, dtype) -> Tuple[int, int, int]:
             raise RuntimeError(f"{name} must be on the same device as query")
         if not t.is_contiguous():
             raise ValueError(f"{name} must be contiguous")
-    if qo.numel() != ko.numel() or qo.dtype != ko.dtype:
+    if qo.dtype != ko.dtype or (qo.numel() != ko.numel() and not shared_kv):
         raise ValueError("query_offset and key_offset must have the same length and dtype")
     return qo.numel() - 1, H, D
 
 
-def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, max_q: int, max_kv: int) -> torch.Tensor:
+def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, max_q: int, max_kv: int,
+                    kv_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     nbytes = _cabi.lib.gdpa_schedule_bytes(mode, total_rows, batch, heads)
     sched = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=qo.device)
     p = _cabi.GdpaSchedParams()
@@ -123,6 +126,8 @@ def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, 
     p.max_seq_len_kv = max_kv
     p.schedule = sched.data_ptr()
     p.schedule_bytes = sched.numel() * 4
+    if kv_index is not None:
+        p.kv_seq_index = kv_index.data_ptr()
     _cabi.check(_cabi.lib.gdpa_build_schedule(C.byref(p), _stream_ptr()), "gdpa_build_schedule")
     return sched
 
@@ -137,6 +142,7 @@ def _fill_fwd_params(q, k, v, o, qo, ko, batch, H, D, max_q, max_kv, scale, act_
     p.batch = batch
     p.total_q, p.total_kv = q.shape[0], k.shape[0]
     p.heads, p.head_dim = H, D
+    p.kv_heads = k.shape[1]  # grouped-query attention when smaller than H
     p.max_seq_len_q, p.max_seq_len_kv = max_q, max_kv
     p.activation = act_id
     p.qk_scale = scale
@@ -203,7 +209,9 @@ def _gdpa_backward_op(
         dv = torch.empty_like(value)
         if batch == 0 or (query.shape[0] == 0 and key.shape[0] == 0):
             return dq, dk, dv
-        sched = _build_schedule(_cabi.GDPA_SCHED_BWD, query_offset, key_offset, batch, H, key.shape[0],
+        # backward work items are (sequence, K/V head, KV tile); with grouped-query attention one item
+        # walks the Q tiles of every query head of its group
+        sched = _build_schedule(_cabi.GDPA_SCHED_BWD, query_offset, key_offset, batch, key.shape[1], key.shape[0],
                                 max_seq_len_q, max_seq_len_kv)
         acc_bytes = _cabi.lib.gdpa_bwd_workspace_bytes(query.shape[0], H, D)
         dq_accum = torch.empty(max(acc_bytes // 4, 1), dtype=torch.float32, device=query.device)
@@ -217,6 +225,7 @@ def _gdpa_backward_op(
         p.batch = batch
         p.total_q, p.total_kv = query.shape[0], key.shape[0]
         p.heads, p.head_dim = H, D
+        p.kv_heads = key.shape[1]
         p.max_seq_len_q, p.max_seq_len_kv = max_seq_len_q, max_seq_len_kv
         p.activation = activation
         p.qk_scale = qk_scale
@@ -304,6 +313,51 @@ def _softmax_backward(ctx, do, dlse):
 
 
 _gdpa_forward_softmax_op.register_autograd(_softmax_backward, setup_context=_softmax_setup_context)
+
+
+@torch.library.custom_op("gdpa::generalized_dot_product_attention_shared_kv", mutates_args=(), device_types="cuda")
+def _gdpa_forward_shared_kv_op(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    query_offset: torch.Tensor,
+    key_offset: torch.Tensor,
+    kv_seq_index: torch.Tensor,
+    max_seq_len_q: int,
+    max_seq_len_kv: int,
+    qk_scale: float,
+    activation: int,
+) -> torch.Tensor:
+    """Forward where Q sequence i attends to KV sequence ``kv_seq_index[i]`` (the reference's
+    ``ad_to_request_offset`` inference path, where many ads share the KV of one request)."""
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16, shared_kv=True)
+    if kv_seq_index.numel() != batch or kv_seq_index.device != query.device:
+        raise ValueError("ad_to_request_offset must hold one KV sequence index per Q sequence, on the device of query")
+    kv_index = kv_seq_index.to(query_offset.dtype).contiguous()
+    with torch.cuda.device(query.device):
+        o = torch.empty_like(query)
+        if query.shape[0] == 0 or batch == 0:
+            return o
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
+                                max_seq_len_q, max_seq_len_kv, kv_index)
+        p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
+                             max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
+        p.kv_seq_index = kv_index.data_ptr()
+        _set_timing(p, "fwd")
+        _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
+    return o
+
+
+@_gdpa_forward_shared_kv_op.register_fake
+def _(query, key, value, query_offset, key_offset, kv_seq_index, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+    return torch.empty_like(query)
+
+
+def _shared_kv_backward(ctx, do):
+    raise NotImplementedError("ad_to_request_offset is an inference path: it has no backward")
+
+
+_gdpa_forward_shared_kv_op.register_autograd(_shared_kv_backward, setup_context=lambda ctx, inputs, output: None)
 
 
 @torch.library.custom_op("gdpa::generalized_dot_product_attention_fp8", mutates_args=(), device_types="cuda")
@@ -398,14 +452,17 @@ def generalized_dot_product_attention(
     """Jagged GDPA: for every sequence b and head h, ``O = (act(Q K^T) * qk_scale) V``.
 
     Same signature as the reference entry point.  ``query`` is ``[total_q, H, D]``, ``key`` and
-    ``value`` are ``[total_kv, H, D]`` (bf16, D in {64, 128}); ``query_offset`` / ``key_offset`` are
+    ``value`` are ``[total_kv, H_kv, D]`` with ``H`` a multiple of ``H_kv`` (grouped-query attention when
+    smaller; bf16, D in {64, 128}); ``query_offset`` / ``key_offset`` are
     ``[B + 1]`` int32 or int64 prefix sums.  ``qk_scale=None`` means 1.0, as in the reference
     (:3148-3149).  ``activation`` is a reference activation name, or ``"softmax"`` (forward and
     backward), for which ``qk_scale`` multiplies the scores before the exponential.
 
     Scheduling knobs of the reference (``seq_index``, ``enable_persistent``, ``enable_tma``,
     ``enable_ws``, ``use_dq_atomic_add``, ``bwd_opt_tech``, ``allow_tf32``, ``total_num_objects``) are
-    accepted and ignored: scheduling is internal.  Every other non-default option raises, as the
+    accepted and ignored: scheduling is internal.  ``ad_to_request_offset`` (one KV sequence index per Q
+    sequence, so that many Q sequences share one KV sequence) is supported for the forward only.  Every
+    other non-default option raises, as the
     reference does for masks and causality (:3138-3139).
     """
     if attn_mask is not None:
@@ -413,7 +470,7 @@ def generalized_dot_product_attention(
     if is_causal:
         raise NotImplementedError("Causal unsupported")
     unsupported = {
-        "ad_to_request_offset": ad_to_request_offset, "attn_offset": attn_offset, "output_offset": output_offset,
+        "attn_offset": attn_offset, "output_offset": output_offset,
         "window_size": window_size, "ts_encoding_params": ts_encoding_params,
         "ts_event_request_even_params": ts_event_request_even_params,
         "ts_event_request_log_params": ts_event_request_log_params,
@@ -437,6 +494,11 @@ def generalized_dot_product_attention(
     query = expect_contiguous(query)
     key = expect_contiguous(key)
     value = expect_contiguous(value)
+    if ad_to_request_offset is not None:
+        return torch.ops.gdpa.generalized_dot_product_attention_shared_kv(
+            query, key, value, query_offset, key_offset, ad_to_request_offset, int(max_seq_len_q), int(max_seq_len_kv),
+            scale, act_id
+        )
     if act_id == SOFTMAX_ID:
         # the trainable softmax variant keeps the log-sum-exp of the forward for its backward
         return torch.ops.gdpa.generalized_dot_product_attention_softmax(

@@ -100,6 +100,11 @@ typedef struct GdpaSchedParams {
   int32_t reserved;
   void* schedule;             /* out: gdpa_schedule_bytes() bytes, 16-byte aligned             */
   int64_t schedule_bytes;     /* size of that buffer                                           */
+  /* Optional [batch] map from a Q sequence to the entry of kv_offsets it attends to (the reference's
+   * ad_to_request_offset: many Q sequences share one KV sequence, forward / inference only;
+   * gdpa/triton/triton_generalized_dot_product_attention.py:3961-3966).  Same integer type as the
+   * offsets.  Null = sequence b reads KV sequence b. */
+  const void* kv_seq_index;
 } GdpaSchedParams;
 
 /* Bytes needed for a schedule of the given pass.  total_rows is total_q for GDPA_SCHED_FWD and
@@ -151,6 +156,13 @@ typedef struct GdpaFwdParams {
    * scores in base 2 (log2 sum_kv 2^(qk_scale log2(e) S)), which gdpa_bwd needs for the softmax
    * backward.  Null = not written. */
   float* lse;
+  /* Grouped-query attention: number of K / V heads (heads must be a multiple of it; query head h reads
+   * K / V head h / (heads / kv_heads)).  0 = same as heads.  K, V (and the FP8 K / V scales) are then
+   * [total_kv, kv_heads, head_dim]. */
+  int32_t kv_heads;
+  int32_t reserved0;
+  /* Optional [batch] map from a Q sequence to its KV sequence, as in GdpaSchedParams (forward only). */
+  const void* kv_seq_index;
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
@@ -218,6 +230,11 @@ typedef struct GdpaBwdParams {
   const void* o;
   const float* lse;
   float* dpsum;
+  /* Grouped-query attention: number of K / V heads, 0 = same as heads.  dK, dV are
+   * [total_kv, kv_heads, head_dim] and sum the contributions of the query heads of a group; the
+   * schedule must have been built with heads = kv_heads. */
+  int32_t kv_heads;
+  int32_t reserved0;
 } GdpaBwdParams;
 
 /* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */

@@ -107,6 +107,12 @@ def gdpa_forward(
         q_i = q[qs:qe].transpose(0, 1)  # [H, Lq, D]
         k_i = k[ks:ke].transpose(0, 1)
         v_i = v[ks:ke].transpose(0, 1)
+        if k_i.shape[0] != q_i.shape[0]:
+            # grouped-query attention: query head h reads K / V head h // group
+            # (off_h_kv = off_h // G, gdpa/triton/triton_generalized_dot_product_attention.py:954)
+            group = q_i.shape[0] // k_i.shape[0]
+            k_i = k_i.repeat_interleave(group, dim=0)
+            v_i = v_i.repeat_interleave(group, dim=0)
         s = torch.matmul(q_i, k_i.transpose(-2, -1))
         if act is None:
             if ke > ks:

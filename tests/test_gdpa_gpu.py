@@ -252,3 +252,59 @@ def test_many_heads_and_int32_offsets_backward(G):
     ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "silu", 1.0 / 32)
     for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
         assert_close(a, b, n)
+
+
+@pytest.mark.parametrize("act", ["gelu_approx", "softmax"])
+@pytest.mark.parametrize("hq,hkv", [(4, 1), (8, 2)])
+def test_grouped_query_attention_forward_backward(G, act, hq, hkv):
+    """H query heads share H_kv key/value heads (query head h reads K/V head h // group); dK and dV
+    sum over the query heads of a group."""
+    lq, lk = [130, 40, 257], [200, 129, 64]
+    g = torch.Generator().manual_seed(91)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]))
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    q = (torch.randn(int(qo[-1]), hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(int(ko[-1]), hkv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(int(ko[-1]), hkv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    do = (torch.randn(int(qo[-1]), hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = G.generalized_dot_product_attention(qd, kd, vd, qo.cuda(), ko.cuda(), max(lq), max(lk), qk_scale=0.1, activation=act)
+    o.backward(do.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    from oracle import gdpa_oracle as orc
+    ro, rdq, rdk, rdv = orc.gdpa_forward_backward(q.float(), k.float(), v.float(), qo, ko, do.float(), act, 0.1)
+    assert kd.grad.shape == k.shape and vd.grad.shape == v.shape
+    for a, b, n in ((o, ro, "O"), (qd.grad, rdq, "dQ"), (kd.grad, rdk, "dK"), (vd.grad, rdv, "dV")):
+        assert_close(a, b, f"{n}[gqa {hq}/{hkv} {act}]")
+
+
+def test_shared_kv_sequences_via_ad_to_request_offset(G):
+    """Many Q sequences ("ads") attend to the KV of one request: Q sequence i reads KV sequence
+    ad_to_request_offset[i], as in the reference's inference path.  Forward only."""
+    lq = [40, 130, 7, 260, 64]
+    lk = [200, 90]                       # two requests
+    ad2req = [0, 0, 1, 0, 1]
+    g = torch.Generator().manual_seed(17)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]))
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    q = (torch.randn(int(qo[-1]), 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(int(ko[-1]), 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(int(ko[-1]), 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    o = G.generalized_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), qo.cuda(), ko.cuda(), max(lq), max(lk),
+                                            ad_to_request_offset=torch.tensor(ad2req).cuda(), qk_scale=0.1,
+                                            activation="gelu_approx")
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    from oracle import gdpa_oracle as orc
+    # oracle: expand the shared KV into one KV sequence per ad
+    k_exp = torch.cat([k[ko[r]:ko[r + 1]] for r in ad2req])
+    v_exp = torch.cat([v[ko[r]:ko[r + 1]] for r in ad2req])
+    ko_exp = torch.tensor(np.concatenate([[0], np.cumsum([lk[r] for r in ad2req])]))
+    ref = orc.gdpa_forward(q.float(), k_exp.float(), v_exp.float(), qo, ko_exp, "gelu_approx", 0.1)
+    assert_close(o, ref, "O[shared KV]")
+    qg = q.cuda().requires_grad_(True)
+    og = G.generalized_dot_product_attention(qg, k.cuda(), v.cuda(), qo.cuda(), ko.cuda(), max(lq), max(lk),
+                                             ad_to_request_offset=torch.tensor(ad2req).cuda(), activation="relu")
+    with pytest.raises(NotImplementedError):
+        og.backward(torch.ones_like(og))
