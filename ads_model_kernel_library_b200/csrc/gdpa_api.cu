@@ -57,15 +57,22 @@ int device_info(DeviceInfo* out) {
 // Tensor map over a [rows, heads, head_dim] row-major tensor; a box is `box_rows` rows of one
 // head by `box_cols` elements, stored with the 128-byte swizzle (box_cols * elem_bytes == 128)
 // or unswizzled.
+// `row_stride` / `head_stride` are in elements; 0 means the contiguous default (heads * head_dim and
+// head_dim).  Packed layouts (Q, K, V interleaved along the last dimension) are views with larger strides.
 int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
-              int head_dim, int box_cols, int box_rows, bool swizzle128) {
+              int head_dim, int box_cols, int box_rows, bool swizzle128, long long row_stride = 0,
+              long long head_stride = 0) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return GDPA_ERR_DRIVER;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  if (head_stride <= 0) head_stride = head_dim;
+  if (row_stride <= 0) row_stride = static_cast<long long>(heads) * head_dim;
+  if (head_stride < head_dim || row_stride < head_stride * heads) return GDPA_ERR_BAD_ARG;
+  if ((head_stride * elem_bytes) % 16 != 0 || (row_stride * elem_bytes) % 16 != 0) return GDPA_ERR_MISALIGNED;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
                         static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim) * elem_bytes,
-                           static_cast<cuuint64_t>(head_dim) * heads * elem_bytes};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_stride) * elem_bytes,
+                           static_cast<cuuint64_t>(row_stride) * elem_bytes};
   cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), 1u, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -205,10 +212,17 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   const void* kp = p->total_kv > 0 ? p->k : p->q;
   const void* vp = p->total_kv > 0 ? p->v : p->q;
   const long long kv_rows = p->total_kv > 0 ? p->total_kv : p->total_q;
-  if ((rc = make_tmap(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  const bool no_kv = p->total_kv == 0;
+  if ((rc = make_tmap(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, kTile, true, p->q_strides[0],
+                      p->q_strides[1])) != GDPA_OK)
+    return rc;
   const int kvh_map = p->total_kv > 0 ? kv_heads : p->heads;
-  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true,
+                      no_kv ? p->q_strides[0] : p->k_strides[0], no_kv ? p->q_strides[1] : p->k_strides[1])) != GDPA_OK)
+    return rc;
+  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true,
+                      no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
+    return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;
   l.args.kv_off = p->kv_offsets;
@@ -285,9 +299,15 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   BwdLaunch l;
   std::memset(&l, 0, sizeof(l));
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if ((rc = make_tmap(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
-  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true, p->q_strides[0],
+                      p->q_strides[1])) != GDPA_OK)
+    return rc;
+  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true, p->k_strides[0],
+                      p->k_strides[1])) != GDPA_OK)
+    return rc;
+  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true, p->v_strides[0],
+                      p->v_strides[1])) != GDPA_OK)
+    return rc;
   if ((rc = make_tmap(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
   // fp32 dQ accumulator, reduced into by 32-column x 32-row boxes (128-byte swizzled staging).
   if ((rc = make_tmap(&l.tm_dq, p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,

@@ -86,6 +86,9 @@ class GdpaFwdParams(C.Structure):
         ("kv_heads", C.c_int32),
         ("reserved0", C.c_int32),
         ("kv_seq_index", C.c_void_p),
+        ("q_strides", C.c_int64 * 2),
+        ("k_strides", C.c_int64 * 2),
+        ("v_strides", C.c_int64 * 2),
     ]
 
 
@@ -122,6 +125,9 @@ class GdpaBwdParams(C.Structure):
         ("dpsum", C.c_void_p),
         ("kv_heads", C.c_int32),
         ("reserved0", C.c_int32),
+        ("q_strides", C.c_int64 * 2),
+        ("k_strides", C.c_int64 * 2),
+        ("v_strides", C.c_int64 * 2),
     ]
 
 

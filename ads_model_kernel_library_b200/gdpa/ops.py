@@ -85,8 +85,10 @@ def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False) -> Tuple[int,
             raise RuntimeError(f"{name} must be a CUDA tensor: this operator has no CPU path")
         if t.dtype != dtype:
             raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
-        if not t.is_contiguous():
-            raise ValueError(f"{name} must be contiguous")
+        if t.stride(2) != 1 or (t.stride(1) * t.element_size()) % 16 or (t.stride(0) * t.element_size()) % 16 \
+                or t.stride(1) < t.shape[2] or t.stride(0) < t.stride(1) * t.shape[1] or t.data_ptr() % 16:
+            raise ValueError(f"{name} must have a contiguous head dimension and 16-byte aligned row / head strides "
+                             "(a contiguous tensor, or a slice of a packed QKV / KV tensor along the last dimension)")
     if k.shape != v.shape:
         raise ValueError("key and value must have the same shape")
     H, D = q.shape[1], q.shape[2]
@@ -142,6 +144,8 @@ def _fill_fwd_params(q, k, v, o, qo, ko, batch, H, D, max_q, max_kv, scale, act_
     p.batch = batch
     p.total_q, p.total_kv = q.shape[0], k.shape[0]
     p.heads, p.head_dim = H, D
+    for field, t in (("q_strides", q), ("k_strides", k), ("v_strides", v)):
+        getattr(p, field)[0], getattr(p, field)[1] = t.stride(0), t.stride(1)
     p.kv_heads = k.shape[1]  # grouped-query attention when smaller than H
     p.max_seq_len_q, p.max_seq_len_kv = max_q, max_kv
     p.activation = act_id
@@ -165,7 +169,7 @@ def _gdpa_forward_op(
 ) -> torch.Tensor:
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
     with torch.cuda.device(query.device):
-        o = torch.empty_like(query)
+        o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         if query.shape[0] == 0 or batch == 0:
             return o
         sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
@@ -179,7 +183,7 @@ def _gdpa_forward_op(
 
 @_gdpa_forward_op.register_fake
 def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
-    return torch.empty_like(query)
+    return query.new_empty(query.shape)
 
 
 @torch.library.custom_op("gdpa::generalized_dot_product_attention_backward", mutates_args=(), device_types="cuda")
@@ -204,9 +208,9 @@ def _gdpa_backward_op(
         raise ValueError("grad_output must have the shape and dtype of query")
     do = do.contiguous()
     with torch.cuda.device(query.device):
-        dq = torch.empty_like(query)
-        dk = torch.empty_like(key)
-        dv = torch.empty_like(value)
+        dq = torch.empty(query.shape, dtype=query.dtype, device=query.device)
+        dk = torch.empty(key.shape, dtype=key.dtype, device=key.device)
+        dv = torch.empty(value.shape, dtype=value.dtype, device=value.device)
         if batch == 0 or (query.shape[0] == 0 and key.shape[0] == 0):
             return dq, dk, dv
         # backward work items are (sequence, K/V head, KV tile); with grouped-query attention one item
@@ -225,6 +229,8 @@ def _gdpa_backward_op(
         p.batch = batch
         p.total_q, p.total_kv = query.shape[0], key.shape[0]
         p.heads, p.head_dim = H, D
+        for field, t in (("q_strides", query), ("k_strides", key), ("v_strides", value)):
+            getattr(p, field)[0], getattr(p, field)[1] = t.stride(0), t.stride(1)
         p.kv_heads = key.shape[1]
         p.max_seq_len_q, p.max_seq_len_kv = max_seq_len_q, max_seq_len_kv
         p.activation = activation
@@ -244,7 +250,7 @@ def _gdpa_backward_op(
 @_gdpa_backward_op.register_fake
 def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, out=None,
       lse=None):
-    return torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+    return query.new_empty(query.shape), key.new_empty(key.shape), value.new_empty(value.shape)
 
 
 def _setup_context(ctx, inputs, output):
@@ -278,7 +284,7 @@ def _gdpa_forward_softmax_op(
     """Softmax forward that also returns the base-2 log-sum-exp ``[H, total_q]`` its backward needs."""
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
     with torch.cuda.device(query.device):
-        o = torch.empty_like(query)
+        o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         lse = torch.zeros((H, query.shape[0]), dtype=torch.float32, device=query.device)
         if query.shape[0] == 0 or batch == 0:
             return o, lse
@@ -294,7 +300,7 @@ def _gdpa_forward_softmax_op(
 
 @_gdpa_forward_softmax_op.register_fake
 def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale):
-    return torch.empty_like(query), torch.empty((query.shape[1], query.shape[0]), dtype=torch.float32, device=query.device)
+    return query.new_empty(query.shape), torch.empty((query.shape[1], query.shape[0]), dtype=torch.float32, device=query.device)
 
 
 def _softmax_setup_context(ctx, inputs, output):
@@ -335,7 +341,7 @@ def _gdpa_forward_shared_kv_op(
         raise ValueError("ad_to_request_offset must hold one KV sequence index per Q sequence, on the device of query")
     kv_index = kv_seq_index.to(query_offset.dtype).contiguous()
     with torch.cuda.device(query.device):
-        o = torch.empty_like(query)
+        o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         if query.shape[0] == 0 or batch == 0:
             return o
         sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
@@ -350,7 +356,7 @@ def _gdpa_forward_shared_kv_op(
 
 @_gdpa_forward_shared_kv_op.register_fake
 def _(query, key, value, query_offset, key_offset, kv_seq_index, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
-    return torch.empty_like(query)
+    return query.new_empty(query.shape)
 
 
 def _shared_kv_backward(ctx, do):
@@ -487,13 +493,25 @@ def generalized_dot_product_attention(
             raise NotImplementedError(f"{name} is not supported by this implementation")
     if use_start_end_offsets or broadcast_q:
         raise NotImplementedError("use_start_end_offsets / broadcast_q are not supported by this implementation")
-    if key is None or value is None:
-        raise NotImplementedError("fused QKV / fused KV layouts are not supported by this implementation")
     act_id = activation_string_to_int(activation)
     scale = 1.0 if qk_scale is None else float(qk_scale)
-    query = expect_contiguous(query)
-    key = expect_contiguous(key)
-    value = expect_contiguous(value)
+    # Packed layouts of the reference (:605-622): query = [T, H, 3D] with key = value = None, or
+    # key = [T, H, 2D] with value = None.  The slices are strided views the kernels read in place.
+    if key is None and value is None:
+        if query.shape[-1] % 3 != 0:
+            raise ValueError("a fused QKV tensor must have a last dimension of 3 * head_dim")
+        query, key, value = expect_contiguous(query).split(query.shape[-1] // 3, dim=-1)
+    elif value is None:
+        if key.shape[-1] % 2 != 0:
+            raise ValueError("a fused KV tensor must have a last dimension of 2 * head_dim")
+        query = expect_contiguous(query)
+        key, value = expect_contiguous(key).split(key.shape[-1] // 2, dim=-1)
+    elif key is None:
+        raise ValueError("value given without key")
+    else:
+        query = expect_contiguous(query)
+        key = expect_contiguous(key)
+        value = expect_contiguous(value)
     if ad_to_request_offset is not None:
         return torch.ops.gdpa.generalized_dot_product_attention_shared_kv(
             query, key, value, query_offset, key_offset, ad_to_request_offset, int(max_seq_len_q), int(max_seq_len_kv),

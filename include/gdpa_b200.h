@@ -163,6 +163,14 @@ typedef struct GdpaFwdParams {
   int32_t reserved0;
   /* Optional [batch] map from a Q sequence to its KV sequence, as in GdpaSchedParams (forward only). */
   const void* kv_seq_index;
+  /* Strides of Q, K, V in elements: {between rows (tokens), between heads}; the head dimension is always
+   * contiguous.  0 = the contiguous default {heads * head_dim, head_dim}.  Packed layouts (the reference's
+   * fused QKV / fused KV tensors, gdpa/triton/triton_generalized_dot_product_attention.py:605-622) are
+   * passed as three base pointers into one buffer with the packed strides.  Strides in bytes must be
+   * multiples of 16.  O is always written contiguously. */
+  int64_t q_strides[2];
+  int64_t k_strides[2];
+  int64_t v_strides[2];
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
@@ -235,6 +243,10 @@ typedef struct GdpaBwdParams {
    * schedule must have been built with heads = kv_heads. */
   int32_t kv_heads;
   int32_t reserved0;
+  /* Strides of Q, K, V in elements, as in GdpaFwdParams (0 = contiguous).  dO, dQ, dK, dV are contiguous. */
+  int64_t q_strides[2];
+  int64_t k_strides[2];
+  int64_t v_strides[2];
 } GdpaBwdParams;
 
 /* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */

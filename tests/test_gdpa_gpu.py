@@ -308,3 +308,42 @@ def test_shared_kv_sequences_via_ad_to_request_offset(G):
                                              ad_to_request_offset=torch.tensor(ad2req).cuda(), activation="relu")
     with pytest.raises(NotImplementedError):
         og.backward(torch.ones_like(og))
+
+
+def test_fused_qkv_and_fused_kv_layouts(G):
+    """The reference's packed layouts: query = [T, H, 3D] with key = value = None (self-attention), and
+    key = [T, H, 2D] with value = None.  The kernels read the slices in place; gradients flow back into
+    the packed tensors."""
+    ln = [70, 200, 129]
+    off = torch.tensor(np.concatenate([[0], np.cumsum(ln)]))
+    g = torch.Generator().manual_seed(23)
+    qkv = (torch.randn(int(off[-1]), 2, 3 * 64, generator=g) * 0.5).to(torch.bfloat16)
+    do = (torch.randn(int(off[-1]), 2, 64, generator=g) * 0.5).to(torch.bfloat16)
+    from oracle import gdpa_oracle as orc
+
+    q, k, v = qkv.float().split(64, dim=-1)
+    ro, rdq, rdk, rdv = orc.gdpa_forward_backward(q, k, v, off, off, do.float(), "gelu_approx", 0.1)
+    x = qkv.cuda().requires_grad_(True)
+    o = G.generalized_dot_product_attention(x, None, None, off.cuda(), off.cuda(), max(ln), max(ln), qk_scale=0.1,
+                                            activation="gelu_approx")
+    o.backward(do.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    assert_close(o, ro, "O[fused QKV]")
+    assert_close(x.grad, torch.cat([rdq, rdk, rdv], dim=-1), "d(QKV)")
+    # fused KV with its own lengths
+    lk = [90, 40, 260]
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    kv = (torch.randn(int(ko[-1]), 2, 2 * 64, generator=g) * 0.5).to(torch.bfloat16)
+    qq = (torch.randn(int(off[-1]), 2, 64, generator=g) * 0.5).to(torch.bfloat16)
+    k2, v2 = kv.float().split(64, dim=-1)
+    ro, rdq, rdk, rdv = orc.gdpa_forward_backward(qq.float(), k2, v2, off, ko, do.float(), "silu", 0.1)
+    xq, xkv = qq.cuda().requires_grad_(True), kv.cuda().requires_grad_(True)
+    o = G.generalized_dot_product_attention(xq, xkv, None, off.cuda(), ko.cuda(), max(ln), max(lk), qk_scale=0.1,
+                                            activation="silu")
+    o.backward(do.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    assert_close(o, ro, "O[fused KV]")
+    assert_close(xq.grad, rdq, "dQ[fused KV]")
+    assert_close(xkv.grad, torch.cat([rdk, rdv], dim=-1), "d(KV)")

@@ -104,8 +104,10 @@ def test_unsupported_options_raise_like_the_reference():
         G.generalized_dot_product_attention(q, q, q, off, off, 4, 4, attn_mask=torch.zeros(1))
     with pytest.raises(NotImplementedError):
         G.generalized_dot_product_attention(q, q, q, off, off, 4, 4, window_size=3)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):  # a fused QKV tensor needs a last dimension of 3 * head_dim
         G.generalized_dot_product_attention(q, None, None, off, off, 4, 4)
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(q, None, q, off, off, 4, 4)
 
 
 def test_token_balanced_shard_planner():
