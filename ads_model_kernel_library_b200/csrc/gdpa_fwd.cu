@@ -2,20 +2,24 @@
 //
 // One persistent CTA per SM walks a longest-first list of work items (sequence, head, 256-row
 // Q block).  A work item keeps two 128-row Q tiles resident in shared memory and streams the
-// sequence's K and V tiles through a shared-memory ring.  Roles (16 warps, registers re-divided
-// with setmaxnreg):
+// sequence's K and V tiles through a shared-memory ring.  Roles (20 warps, 96 registers each):
 //
-//   warps 0-3   activation group 0: S0 (TMEM) -> registers -> act * scale -> bf16 P0 (TMEM)
-//   warps 4-7   activation group 1: same for S1
-//   warps 8-11  epilogue: O0 / O1 (TMEM) -> registers -> bf16 -> global
-//   warp  12    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
+//   warps 0-7   activation of Q tile 0: S0 (TMEM) -> registers -> act * scale -> bf16 P0 (TMEM); two
+//               warps per TMEM lane quarter, each owning 64 of the 128 S columns.  At the end of a work
+//               item the same warps drain their half of O0 (TMEM -> bf16 -> global).
+//   warps 8-15  the same for Q tile 1
+//   warp  16    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
 //               O_s += P_s V (A operand P read from TMEM)
-//   warp  13    TMA loader (one lane);  warps 14-15 idle (they complete the fourth warpgroup)
+//   warp  17    TMA loader (one lane);  warps 18-19 idle
 //
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).  P_s (bf16, two
-// values per column) overwrites the first 64 columns of S_s once those have been read.
-// While one activation group works on its S tile the tensor cores run the other group's P V and
+// values per column) of column half h overwrites the first 32 columns of that half's own S columns.
+// While the warps of one Q tile run their activation the tensor cores run the other tile's P V and
 // next Q K^T, so activation and MMA overlap.
+//
+// Variants of the same kernel: softmax with online rescaling (the two column halves exchange their row
+// maxima through shared memory, keep partial row sums and write the log-sum-exp for the backward), and
+// FP8 e4m3 operands with per-128-token-block scales (softmax only).
 //
 // Rows of a tile that lie beyond the end of a sequence hold other sequences' tokens (or zeros
 // past the end of the tensor): S columns beyond the KV length are set to zero before the
@@ -28,19 +32,12 @@ namespace gdpa {
 
 namespace {
 
-// Two warp layouts.
-//  narrow (16 warps): warps 0-3 / 4-7 activation of Q tile 0 / 1 (a thread owns a whole 128-column row of
-//    S), warps 8-11 epilogue, 12 MMA, 13 TMA, 14-15 idle.  Used by softmax and FP8, whose row statistics
-//    want a whole row per thread.
-//  wide (20 warps): warps 0-7 / 8-15 activation of Q tile 0 / 1 (two warps per TMEM lane quarter, each
-//    owning 64 of the 128 S columns; they also drain their half of O at the end of a work item), 16 MMA,
-//    17 TMA, 18-19 idle; every warp keeps the 96 registers of the launch.  A single warp cannot overlap its MUFU instructions with its FMA-pipe
-//    instructions, so two activation warps per SM sub-partition and Q tile halve the activation time.
-constexpr int kFwdRegsAct = 152;
-constexpr int kFwdRegsEpi = 104;
-constexpr int kFwdRegsOther = 104;
+// 20 warps: warps 0-7 / 8-15 activation of Q tile 0 / 1 (two warps per TMEM lane quarter, each owning 64
+// of the 128 S columns; they also drain their half of O at the end of a work item), 16 MMA, 17 TMA,
+// 18-19 idle.  A single warp cannot overlap its MUFU instructions with its FMA-pipe instructions, so two
+// activation warps per SM sub-partition and Q tile halve the activation time.
+constexpr int kFwdThreads = 20 * 32;
 constexpr int kKvStages = 4;
-__host__ __device__ constexpr int fwd_threads(bool wide) { return wide ? 20 * 32 : 16 * 32; }
 
 // Barrier indices inside the shared barrier array.
 enum FwdBar : int {
@@ -78,16 +75,16 @@ struct FwdSmem {
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
     goto role_done;
 
-template <int D, int ACT, bool FP8, bool WIDE>
-__global__ void __launch_bounds__(fwd_threads(WIDE), 1)
+template <int D, int ACT, bool FP8>
+__global__ void __launch_bounds__(kFwdThreads, 1)
 gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
-  constexpr int kActWarps = WIDE ? 16 : 8;
-  constexpr int kMmaWarp = WIDE ? 16 : 12;
-  constexpr int kLoadWarp = WIDE ? 17 : 13;
-  constexpr uint32_t kStageThreads = WIDE ? 256u : 128u;  // threads that work on one Q tile's S / O
+  constexpr int kActWarps = 16;
+  constexpr int kMmaWarp = 16;
+  constexpr int kLoadWarp = 17;
+  constexpr uint32_t kStageThreads = 256u;  // threads that work on one Q tile's S / O
   using L = FwdSmem<D, EB>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -136,7 +133,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t kIdescPV = umma_idesc(kFmt, kFmt, 0, 1, kTile, D);
 
   if (warp >= kMmaWarp) {
-   if constexpr (!WIDE) setmaxnreg_dec<kFwdRegsOther>();
    if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA loader
     if (lane == 0) {
@@ -213,8 +209,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
           const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
-          // wide layout: the P slices of column half h sit at the start of that half's own S columns
-          const uint32_t a_col = !WIDE ? kk * 8 : (FP8 ? (kk >> 1) * 64 + (kk & 1) * 8 : (kk >> 2) * 64 + (kk & 3) * 8);
+          // the P slices of column half h sit at the start of that half's own S columns
+          const uint32_t a_col = FP8 ? (kk >> 1) * 64 + (kk & 1) * 8 : (kk >> 2) * 64 + (kk & 3) * 8;
           if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
           else umma_ts_f16(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
         }
@@ -279,8 +275,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
    }
-  } else if (WIDE && warp < kActWarps) {
-    // ------------------------------------------------------------------ activation + epilogue (wide)
+  } else if (warp < kActWarps) {
+    // ------------------------------------------------------------------ activation + epilogue
     const int s = warp >> 3;           // Q tile
     const int half = (warp >> 2) & 1;  // which 64 of the 128 S columns
     const int row = (warp & 3) * 32 + lane;
@@ -312,7 +308,10 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if constexpr (kSoftmax) {
         // ---- softmax, one row split over two warps (64 columns each): the halves publish their partial
         // row maxima through shared memory and an mbarrier, take the common maximum, and keep partial row
-        // sums that the epilogue adds.  Otherwise as in the narrow layout.
+        // sums that the epilogue adds.  P = exp2(c S + bias - m); the O accumulator is rescaled only when
+        // the running maximum m grew by more than kThr.  FP8: c carries the Q- and K-block scales and
+        // bias = log2(V-block scale), so P contains the V scale and uses the whole e4m3 range; the row
+        // sum divides it out again.
         constexpr float kThr = FP8 ? 1.f : 8.f;
         constexpr float kPScale = FP8 ? 128.f : 1.f;
         constexpr float kLog2e = 1.4426950408889634f;
@@ -493,229 +492,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-  } else if (!WIDE && warp < 8) {
-    // ------------------------------------------------------------------ activation groups
-    setmaxnreg_inc<kFwdRegsAct>();
-    const int s = warp >> 2;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_base + s * kTile;
-    const float scale = a.scale, hscale = 0.5f * a.scale;
-    uint32_t s_phase = 0;
-    int tr = 0;  // trace: KV blocks seen so far by this role (slot layout: see GDPA_TRACE uses)
-    WorkWalker walker(n_items);
-    int idx;
-    while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
-      const int nkv = (w.lkv + kTile - 1) / kTile;
-      const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
-      if (nkv == 0 || s >= nst) continue;
-      if constexpr (kSoftmax) {
-        // ---- softmax with online rescaling: P = exp2(c S + bias - m), O rescaled when the running
-        // row maximum m grows by more than kThr, row sums kept in fp32 and divided out by the epilogue.
-        // FP8: c carries the Q- and K-block scales, bias = log2(V-block scale), so that P already
-        // contains the V scale and uses the whole e4m3 range; the row sum divides it out again.
-        constexpr float kThr = FP8 ? 1.f : 8.f;
-        constexpr float kPScale = FP8 ? 128.f : 1.f;
-        constexpr float kLog2e = 1.4426950408889634f;
-        float m_used = -INFINITY, row_sum = 0.f;
-        float sq = 1.f;
-        long long kv_blk0 = 0;
-        if constexpr (FP8) {
-          sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
-          kv_blk0 = load_offset(a.kv_blk_off, a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, w.b, a.off64)) : w.b, a.off64);
-        }
-        const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
-        for (int j = 0; j < nkv; ++j) {
-          const int valid = min(kTile, w.lkv - j * kTile);
-          float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
-          if constexpr (FP8) {
-            const float sk = a.k_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
-            const float sv = a.v_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
-            c *= sq * sk;
-            bias = log2f(sv);
-            inv_sv = 1.f / sv;
-          }
-          GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
-          s_phase ^= 1u;
-          tc_fence_after();
-          uint32_t ra[32], rb[32];
-          // pass 1: row maximum of c * S over the valid columns
-          float rmax = -INFINITY;
-          tmem_ld32(s_tmem, ra);
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t(&cur)[32] = (ch & 1) ? rb : ra;
-            uint32_t(&nxt)[32] = (ch & 1) ? ra : rb;
-            tmem_wait_ld();
-            tmem_regs_ready(cur);
-            if (ch < 3) tmem_ld32(s_tmem + (ch + 1) * 32, nxt);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float t = __uint_as_float(cur[i]) * c;
-              rmax = (ch * 32 + i < valid) ? fmaxf(rmax, t) : rmax;
-            }
-          }
-          const float m_new = fmaxf(m_used, rmax + bias);
-          if (j == 0) {
-            m_used = m_new;
-          } else if (__any_sync(0xffffffffu, m_new > m_used + kThr)) {
-            // rescale this warp's O rows (PV of the previous KV tile has completed: the commit that
-            // released this S tile was issued after it)
-            const float alpha = ex2_approx(m_used - m_new);
-            row_sum *= alpha;
-            m_used = m_new;
-#pragma unroll
-            for (int ch = 0; ch < D / 32; ++ch) {
-              tmem_ld32(o_tmem + ch * 32, ra);
-              tmem_wait_ld();
-              tmem_regs_ready(ra);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) ra[i] = __float_as_uint(__uint_as_float(ra[i]) * alpha);
-              tmem_st32(o_tmem + ch * 32, ra);
-            }
-          }
-          // pass 2: P = exp2(c S + bias - m), row sum, quantise, store over the S columns already read
-          const float off = bias - m_used;
-          float psum = 0.f;
-          tmem_ld32(s_tmem, ra);
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t(&cur)[32] = (ch & 1) ? rb : ra;
-            uint32_t(&nxt)[32] = (ch & 1) ? ra : rb;
-            tmem_wait_ld();
-            tmem_regs_ready(cur);
-            if (ch < 3) tmem_ld32(s_tmem + (ch + 1) * 32, nxt);
-            float pv[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
-              pv[i] = (ch * 32 + i < valid) ? e : 0.f;
-              psum += pv[i];
-            }
-            if constexpr (FP8) {
-              uint32_t pk[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                pk[i] = pack_e4m3x4(pv[4 * i] * kPScale, pv[4 * i + 1] * kPScale, pv[4 * i + 2] * kPScale, pv[4 * i + 3] * kPScale);
-              tmem_st8(s_tmem + ch * 8, pk);
-            } else {
-              uint32_t pk[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
-              tmem_st16(s_tmem + ch * 16, pk);
-            }
-          }
-          row_sum = fmaf(psum, inv_sv, row_sum);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar_base + 8u * (B_P_FULL + s));
-        }
-        // hand the row sum to the epilogue (it divides O by it)
-        reinterpret_cast<float*>(smem + L::kRowSumOff)[s * 2 * kTile + (warp & 3) * 32 + lane] = row_sum * kPScale;
-        mbar_arrive(bar_base + 8u * (B_L_FULL + s));
-        continue;
-      }
-      for (int j = 0; j < nkv; ++j) {
-        const int valid = min(kTile, w.lkv - j * kTile);  // valid KV columns of this tile
-        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
-        GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
-        s_phase ^= 1u;
-        tc_fence_after();
-        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 1);
-        // Four 32-column chunks; the TMEM load of chunk c+1 is in flight while chunk c is computed.
-        uint32_t ra[32], rb[32];
-        tmem_ld32(s_tmem, ra);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-          uint32_t pk[16];
-          tmem_wait_ld();
-          tmem_regs_ready(cur);
-          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
-          if (valid >= (c + 1) * 32) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[i] = act_scaled_pair_bf16<ACT>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(cur[2 * i]) : 0.f;
-              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(cur[2 * i + 1]) : 0.f;
-              pk[i] = act_scaled_pair_bf16<ACT>(x0, x1, scale, hscale);
-            }
-          }
-          tmem_st16(s_tmem + c * 16, pk);
-        }
-        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 2);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_base + 8u * (B_P_FULL + s));
-        if ((threadIdx.x & 127) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 3);
-        ++tr;
-      }
-    }
-  } else if (!WIDE) {
-    // ------------------------------------------------------------------ epilogue (warps 8-11)
-    setmaxnreg_dec<kFwdRegsEpi>();
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t o_phase[2] = {0, 0};
-    WorkWalker walker(n_items);
-    int idx;
-    while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
-      const int nkv = (w.lkv + kTile - 1) / kTile;
-      const int q0 = w.blk * kFwdQBlock;
-      const int nst = (w.lq - q0 > kTile) ? 2 : 1;
-      for (int s = 0; s < nst; ++s) {
-        const int qr = q0 + s * kTile + row;
-        const bool valid = qr < w.lq;
-        uint4* dst = reinterpret_cast<uint4*>(a.o + ((w.q_start + qr) * a.heads + w.h) * static_cast<long long>(D));
-        if (nkv == 0) {
-          if (valid) {
-#pragma unroll
-            for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
-          }
-          continue;
-        }
-        GDPA_WAIT(B_O_FULL + s, o_phase[s], ST_ROLE_EPI);
-        float inv_l = 1.f;
-        if constexpr (kSoftmax) {
-          GDPA_WAIT(B_L_FULL + s, o_phase[s], ST_ROLE_EPI);
-          inv_l = 1.f / reinterpret_cast<volatile float*>(smem + L::kRowSumOff)[s * 2 * kTile + row];
-        }
-        o_phase[s] ^= 1u;
-        tc_fence_after();
-        const uint32_t o_tmem = tmem_base + lane_base + 256 + s * kTile;
-        uint32_t ra[32], rb[32];
-        tmem_ld32(o_tmem, ra);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
-          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
-          tmem_wait_ld();
-          tmem_regs_ready(cur);
-          if (c < D / 32 - 1) {
-            tmem_ld32(o_tmem + (c + 1) * 32, nxt);
-          } else {
-            tc_fence_before();
-            mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
-          }
-          if (valid) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(cur[8 * i + 0]) * inv_l, __uint_as_float(cur[8 * i + 1]) * inv_l);
-              v.y = pack_bf16x2(__uint_as_float(cur[8 * i + 2]) * inv_l, __uint_as_float(cur[8 * i + 3]) * inv_l);
-              v.z = pack_bf16x2(__uint_as_float(cur[8 * i + 4]) * inv_l, __uint_as_float(cur[8 * i + 5]) * inv_l);
-              v.w = pack_bf16x2(__uint_as_float(cur[8 * i + 6]) * inv_l, __uint_as_float(cur[8 * i + 7]) * inv_l);
-              dst[c * 4 + i] = v;
-            }
-          }
-        }
-      }
-    }
   }
 
 role_done:
@@ -734,11 +510,10 @@ role_done:
 template <int D, int ACT, bool FP8>
 int launch_fwd_inst(const FwdLaunch& l) {
   using L = FwdSmem<D, FP8 ? 1 : 2>;
-  constexpr bool kWide = true;  // the narrow layout (kWide = false) remains instantiable for comparison
-  auto kernel = gdpa_fwd_kernel<D, ACT, FP8, kWide>;
+  auto kernel = gdpa_fwd_kernel<D, ACT, FP8>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
-  kernel<<<l.grid, fwd_threads(kWide), L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
+  kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 
