@@ -84,14 +84,12 @@ struct BwdSmem {
 
 // How dQ tiles leave the SM: staged in shared memory and added by TMA reduce (full 128-byte lines at
 // L2, but 128 KB of shared-memory traffic per tile), or straight from registers with vector reductions.
-// Where the A operand of dK comes from: TMEM (32 KB less shared-memory traffic per Q tile, but dK must be
-// issued before dQ, so nothing hides the drain of dQ) or shared memory (dK runs while dQ is drained).
-constexpr bool kDkFromTmem = true;  // measured: 4 815 vs 4 957 cycles per Q tile
-constexpr bool kDqViaTma = true;  // measured: 793 vs 578 TFLOP/s (backward, B=512 uniform workload)
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
+// Two alternatives were measured on the B=512 uniform workload and dropped.  (1) Adding dQ tiles to the
+// accumulator straight from registers with red.global.add.v4.f32 (no shared-memory staging): 578 instead
+// of 803 TFLOP/s, the 16-byte reductions to 32 different 128-byte lines per instruction saturate the
+// LSU / L2 path.  (2) Reading the A operand of dK from shared memory and issuing dQ before dK (the drain
+// of dQ then overlaps dK, at 32 KB more shared-memory traffic per Q tile): 4 957 instead of 4 815 cycles
+// per Q tile.
 
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
@@ -244,31 +242,19 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               ds_phase ^= 1u;
               tc_fence_after();
               GDPA_TRACE(a, tr * 32 + 2);
-              if constexpr (kDkFromTmem) {
-                // dK += dS^T Q_{m-1} : A = dS^T (bf16 in TMEM over the dP^T columns this half has read),
-                // B = Q tile MN-major.  Issued before dQ, which overwrites those columns.
+              // dK += dS^T Q_{m-1} : A = dS^T (bf16 in TMEM over the dP^T columns this half has read),
+              // B = Q tile MN-major.  Issued before dQ, which overwrites those columns.
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)
-                  umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
-                              umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
-                              (m > 1 || kk > 0) ? 1u : 0u);
-              }
+              for (int kk = 0; kk < kTile / 16; ++kk)
+                umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            (m > 1 || kk > 0) ? 1u : 0u);
               // dQ_{m-1} = dS K : A = dS^T tile in shared memory read MN-major, B = K tile MN-major
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
                 umma_ss_f16(tmem_base + kColDP, umma_smem_desc_sw128(sDs + kk * 2048, L::kHalfBytes, 1024),
                             umma_smem_desc_sw128(sK + kk * 2048, L::kHalfBytes, 1024), kIdescMM, kk > 0 ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DQ_FULL);
-              if constexpr (!kDkFromTmem) {
-                // dK += dS^T Q_{m-1} : A = dS^T in shared memory, K-major over q; runs while dQ is drained
-#pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk) {
-                  const uint32_t aoff = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
-                  umma_ss_f16(tmem_base + kColDK, umma_smem_desc_sw128(sDs + aoff, 16, 1024),
-                              umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
-                              (m > 1 || kk > 0) ? 1u : 0u);
-                }
-              }
               tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
               GDPA_TRACE(a, tr * 32 + 3);
             }
@@ -456,9 +442,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[4 * j + 3] = d[3];
           }
           // the same values as the A operand of dK, over dP^T columns this half has already read
-          if constexpr (kDkFromTmem) tmem_st16(tDP + half * 64 + c * 16, pk);
+          tmem_st16(tDP + half * 64 + c * 16, pk);
         }
-        if constexpr (kDkFromTmem) tmem_wait_st();
+        tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DS_FULL);
@@ -532,38 +518,23 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 15);
-        if constexpr (kDqViaTma) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            const uint32_t buf = slab & 1u;
-            // the reduce that read this staging buffer two slabs ago must have finished reading it
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
+        for (int c = 0; c < D / 32; ++c) {
+          const uint32_t buf = slab & 1u;
+          // the reduce that read this staging buffer two slabs ago must have finished reading it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
-                  make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
-              tma_store_commit();
-            }
-            ++slab;
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
+            tma_store_commit();
           }
-        } else {
-          // straight from registers: one 16-byte vector reduction per lane and 4 columns; rows beyond
-          // the sequence are skipped (their values are zero anyway)
-          const int q_local = mm * kTile + warp * 32 + lane;
-          if (q_local < w.lq) {
-            float* dst = a.dq_accum + ((w.q_start + q_local) * a.q_heads + hq) * static_cast<long long>(D);
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c)
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(r[c][4 * j]), __uint_as_float(r[c][4 * j + 1]),
-                           __uint_as_float(r[c][4 * j + 2]), __uint_as_float(r[c][4 * j + 3]));
-          }
+          ++slab;
         }
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 16);
         ++tr;
