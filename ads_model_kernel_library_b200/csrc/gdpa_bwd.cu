@@ -94,6 +94,13 @@ struct BwdSmem {
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
     goto role_done;
+// The same for roles whose whole warp waits and then executes warp-collective tcgen05.ld / st: the
+// decision to leave is taken by the warp as a whole, so no lane runs ahead into a collective instruction.
+#define GDPA_WAIT_WARP(bar_idx, parity, role)                                                                       \
+  {                                                                                                                 \
+    const bool ok_ = mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role)); \
+    if (!__all_sync(0xffffffffu, ok_)) goto role_done;                                                              \
+  }
 
 template <int D, int ACT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -348,7 +355,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             stat = (ew_tid < 128) ? a.lse[at] : a.dpsum[at];
           }
         }
-        GDPA_WAIT(BB_S_FULL, s_phase, ST_ROLE_ACT);
+        GDPA_WAIT_WARP(BB_S_FULL, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
         if (tracer) GDPA_TRACE(a, tr * 32 + 9);
@@ -358,7 +365,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (ew_tid < 128) stat_lse[ew_tid] = stat;
           else stat_dps[(m & 1) * kTile + (ew_tid - 128)] = stat;
           mbar_arrive(bar_base + 8u * BB_ST_FULL);
-          GDPA_WAIT(BB_ST_FULL, st_phase, ST_ROLE_ACT);
+          GDPA_WAIT_WARP(BB_ST_FULL, st_phase, ST_ROLE_ACT);
           st_phase ^= 1u;
         }
         tmem_ld32(tS + half * 64, ra);
@@ -403,7 +410,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive(bar_base + 8u * BB_P_FULL);
         if (tracer) GDPA_TRACE(a, tr * 32 + 10);
 
-        GDPA_WAIT(BB_DP_FULL, dp_phase, ST_ROLE_ACT);
+        GDPA_WAIT_WARP(BB_DP_FULL, dp_phase, ST_ROLE_ACT);
         dp_phase ^= 1u;
         tc_fence_after();
         if (tracer) GDPA_TRACE(a, tr * 32 + 11);
@@ -452,7 +459,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ++tr;
       }
       // dK / dV of this KV tile: TMEM -> bf16 -> global, rows inside the sequence only.
-      GDPA_WAIT(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
+      GDPA_WAIT_WARP(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
       dkv_phase ^= 1u;
       tc_fence_after();
 #pragma unroll
@@ -544,6 +551,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 role_done:
   __syncwarp();
+  if (*abort_flag != 0) {
+    // a wait ran out: give this CTA's TMA copies and MMAs in flight a bounded time (1 ms) to finish
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 1000000ull) {}
+  }
   if (warp < 4 && lane == 0) tma_store_wait_all<0>();  // this warp's reduce-adds have left shared memory
   tc_fence_before();
   __syncthreads();
@@ -554,6 +566,7 @@ role_done:
 }
 
 #undef GDPA_WAIT
+#undef GDPA_WAIT_WARP
 
 __global__ void __launch_bounds__(256) gdpa_dq_convert_kernel(const float4* __restrict__ acc, uint2* __restrict__ dq,
                                                               long long n4) {

@@ -74,6 +74,13 @@ struct FwdSmem {
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
     goto role_done;
+// The same for roles whose whole warp waits and then executes warp-collective tcgen05.ld / st: the
+// decision to leave is taken by the warp as a whole, so no lane runs ahead into a collective instruction.
+#define GDPA_WAIT_WARP(bar_idx, parity, role)                                                                       \
+  {                                                                                                                 \
+    const bool ok_ = mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role)); \
+    if (!__all_sync(0xffffffffu, ok_)) goto role_done;                                                              \
+  }
 
 template <int D, int ACT, bool FP8>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -334,7 +341,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             bias = log2f(sv);
             inv_sv = 1.f / sv;
           }
-          GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+          GDPA_WAIT_WARP(B_S_FULL + s, s_phase, ST_ROLE_ACT);
           tc_fence_after();
           uint32_t ra[32], rb[32];
           // pass 1: partial row maximum of c * S over this warp's valid columns (chunk 1 in flight
@@ -356,7 +363,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           float* slot = rowmax + (((s_phase * 2 + s) * 2) * kTile);
           slot[half * kTile + row] = pmax;
           mbar_arrive(bar_base + 8u * (B_M_FULL + s));
-          GDPA_WAIT(B_M_FULL + s, s_phase, ST_ROLE_ACT);
+          GDPA_WAIT_WARP(B_M_FULL + s, s_phase, ST_ROLE_ACT);
           const float rmax = fmaxf(pmax, reinterpret_cast<volatile float*>(slot)[(half ^ 1) * kTile + row]);
           s_phase ^= 1u;
           const float m_new = fmaxf(m_used, rmax + bias);
@@ -420,7 +427,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // both halves publish their partial row sums; each then divides its half of O by the total
         rowsum[(s * 2 + half) * kTile + row] = row_sum * kPScale;
         mbar_arrive(bar_base + 8u * (B_L_FULL + s));
-        GDPA_WAIT(B_L_FULL + s, o_phase, ST_ROLE_EPI);
+        GDPA_WAIT_WARP(B_L_FULL + s, o_phase, ST_ROLE_EPI);
         inv_l = 1.f / (row_sum * kPScale + reinterpret_cast<volatile float*>(rowsum)[(s * 2 + (half ^ 1)) * kTile + row]);
         if constexpr (!FP8) {
           // log-sum-exp of the scaled scores in base 2, for the softmax backward
@@ -431,7 +438,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int j = 0; !kSoftmax && j < nkv; ++j) {
         const int valid = min(kTile, w.lkv - j * kTile) - half * 64;  // valid columns among this warp's 64
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
-        GDPA_WAIT(B_S_FULL + s, s_phase, ST_ROLE_ACT);
+        GDPA_WAIT_WARP(B_S_FULL + s, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
         tc_fence_after();
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 1);
@@ -466,7 +473,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ++tr;
       }
       // epilogue: this warp's half of the O tile, TMEM -> bf16 -> global
-      GDPA_WAIT(B_O_FULL + s, o_phase, ST_ROLE_EPI);
+      GDPA_WAIT_WARP(B_O_FULL + s, o_phase, ST_ROLE_EPI);
       o_phase ^= 1u;
       tc_fence_after();
 #pragma unroll
@@ -497,6 +504,11 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 role_done:
   // Teardown: everyone meets here (also after a wait ran out), then the allocating warp frees TMEM.
   __syncwarp();
+  if (*abort_flag != 0) {
+    // a wait ran out: give this CTA's TMA copies and MMAs in flight a bounded time (1 ms) to finish
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 1000000ull) {}
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -506,6 +518,7 @@ role_done:
 }
 
 #undef GDPA_WAIT
+#undef GDPA_WAIT_WARP
 
 template <int D, int ACT, bool FP8>
 int launch_fwd_inst(const FwdLaunch& l) {
