@@ -15,11 +15,17 @@ against outputs of the reference's own Python code run on the CPU (committed und
   gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:35-47, with the activation table
   ``get_pytorch_activation``, gdpa/triton/math.py:58-74.
 
-What those two do not pin (the reference has no CPU code for it) is the placement of
-``qk_scale``; it follows the reference's device kernels: ``p = act(qk); p *= qk_scale``
-(gdpa/triton/triton_generalized_dot_product_attention.py:279-307) and, in the backward,
-``dS = qk_scale * act'(S) * dP`` (:1626-1634).  Gradients come from autograd over the forward
-below, which is the same chain rule.
+* the reference's Triton forward and backward kernels themselves
+  (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335, :3461-3788) executed on the CPU
+  by Triton's interpreter, with ``qk_scale = 0.25``, different Q and KV lengths and a grouped-query
+  case: O, dQ, dK, dV for raw, gelu_approx, leaky_relu, relu, silu, hardswish, relu_square (the other
+  activations are written with inline PTX, which the interpreter cannot run).
+
+The last item pins where ``qk_scale`` is applied (``p = act(qk); p *= qk_scale``, :279-307) and every
+gradient (``dS = qk_scale * act'(S) * dP``, :1626-1634); gradients here come from autograd over the
+forward below, which is the same chain rule.  Not pinned by reference outputs: the softmax backward
+(the reference has none) and the FP8 block-scaled variant (no CPU or interpreter path in the
+reference); both are checked against this fp32 restatement only.
 """
 from __future__ import annotations
 

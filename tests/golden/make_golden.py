@@ -4,7 +4,7 @@ code on the CPU.  Needs a checkout of the reference; run as
     python tests/golden/make_golden.py /path/to/ads_model_kernel_library
 
 The reference uses absolute imports ``ads_mkl.ops.oss.<package>``; a temporary directory with a
-symlink of that name makes them resolve.  Three things are recorded:
+symlink of that name makes them resolve.  Four things are recorded:
 
 * ``reference_cpu_softmax``: outputs of ``cpu_generalized_dot_product_attention``
   (gdpa/triton/triton_generalized_dot_product_attention.py:3898-3979) on a jagged batch with
@@ -14,6 +14,12 @@ symlink of that name makes them resolve.  Three things are recorded:
   with the reference's activation table ``get_pytorch_activation`` (gdpa/triton/math.py:58-74);
   the helper's module cannot be imported whole because it needs a Triton fork, so the single
   function is taken from its source by ``ast`` and executed unchanged;
+* ``triton_<activation>_{o,dq,dk,dv}``: outputs of the reference's Triton GDPA kernels themselves, the
+  forward op body (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335) and the backward
+  op body (:3461-3788), executed on the CPU by Triton's interpreter (``TRITON_INTERPRET=1``, autotuning
+  off), on a jagged batch with different Q and KV lengths and ``qk_scale = 0.25``, for every activation
+  of the table; plus one grouped-query case (4 query heads, 2 K/V heads).  These pin where the scale is
+  applied and every gradient;
 * ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
 
 Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
@@ -25,6 +31,12 @@ import json
 import os
 import sys
 import tempfile
+
+# The Triton kernels of the reference run on the CPU through Triton's interpreter; both switches must be
+# set before triton is imported.
+os.environ.setdefault("TRITON_INTERPRET", "1")
+os.environ.setdefault("GDPA_DISABLE_AUTOTUNE", "1")
+os.environ.setdefault("ADS_MKL_DISABLE_AUTOTUNE", "1")
 
 import numpy as np
 import torch
@@ -82,11 +94,55 @@ def main(ref_root: str) -> None:
     for act in ref_math.Activation:
         out[f"eager_out_{act.value}"] = helper(q, k, v, off, act).numpy()
 
+    # ---- 3. the Triton forward and backward kernels under the interpreter --------------------
+    from torch._library.custom_ops import OPDEFS
+
+    fwd = OPDEFS["gdpa::generalized_dot_product_attention"]._init_fn
+    bwd = OPDEFS["gdpa::generalized_dot_product_attention_backward"]._init_fn
+    rng = np.random.default_rng(777)
+    B, H, D = 3, 2, 16
+    lq, lk = rng.integers(1, 40, B), rng.integers(1, 50, B)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]), dtype=torch.int32)
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]), dtype=torch.int32)
+    g = torch.Generator().manual_seed(777)
+    q = torch.randn(int(qo[-1]), H, D, generator=g)
+    k = torch.randn(int(ko[-1]), H, D, generator=g)
+    v = torch.randn(int(ko[-1]), H, D, generator=g)
+    do = torch.randn(int(qo[-1]), H, D, generator=g)
+    scale = 0.25
+    out.update(triton_q=q.numpy(), triton_k=k.numpy(), triton_v=v.numpy(), triton_do=do.numpy(),
+               triton_qo=qo.numpy(), triton_ko=ko.numpy(), triton_scale=np.float32(scale))
+    skipped = []
+    for act in ref_math.Activation:
+        try:
+            o = fwd(q, k, v, qo, ko, int(lq.max()), int(lk.max()), qk_scale=scale, activation=act.value)
+            res = bwd(do, q, k, v, o, qo, ko, B, H, 1, int(lq.max()), int(lk.max()), D, D, qk_scale=scale,
+                      activation_enum_int=ref_math.activation_to_int[act])
+        except Exception as e:  # activations written with inline PTX cannot run in the interpreter
+            skipped.append(act.value)
+            continue
+        out[f"triton_{act.value}_o"] = o.numpy()
+        out[f"triton_{act.value}_dq"] = res[0].numpy()
+        out[f"triton_{act.value}_dk"] = res[1].numpy()
+        out[f"triton_{act.value}_dv"] = res[2].numpy()
+    # grouped-query attention: 4 query heads over 2 K/V heads (Q_GROUP = 2)
+    Hq, G = 4, 2
+    qg = torch.randn(int(qo[-1]), Hq, D, generator=g)
+    kg = torch.randn(int(ko[-1]), Hq // G, D, generator=g)
+    vg = torch.randn(int(ko[-1]), Hq // G, D, generator=g)
+    dog = torch.randn(int(qo[-1]), Hq, D, generator=g)
+    og = fwd(qg, kg, vg, qo, ko, int(lq.max()), int(lk.max()), qk_scale=scale, activation="gelu_approx")
+    resg = bwd(dog, qg, kg, vg, og, qo, ko, B, Hq, G, int(lq.max()), int(lk.max()), D, D, qk_scale=scale,
+               activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
+    out.update(gqa_q=qg.numpy(), gqa_k=kg.numpy(), gqa_v=vg.numpy(), gqa_do=dog.numpy(), gqa_o=og.numpy(),
+               gqa_dq=resg[0].numpy(), gqa_dk=resg[1].numpy(), gqa_dv=resg[2].numpy())
+
     np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
     ids = {a.value: i for a, i in ref_math.activation_to_int.items()}
     with open(os.path.join(HERE, "activation_ids.json"), "w") as f:
         json.dump(ids, f, indent=1)
     print("wrote", len(out), "arrays;", ids)
+    print("activations the Triton interpreter could not run (inline PTX):", skipped)
 
 
 if __name__ == "__main__":
