@@ -103,6 +103,7 @@ int check_common(const P* p) {
   if (p == nullptr || p->struct_size != sizeof(P)) return GDPA_ERR_BAD_ARG;
   if (p->batch < 0 || p->heads <= 0 || p->total_q < 0 || p->total_kv < 0) return GDPA_ERR_BAD_ARG;
   if (p->max_seq_len_q < 0 || p->max_seq_len_kv < 0) return GDPA_ERR_BAD_ARG;
+  if (p->window_plus_one < 0 || p->window_plus_one > (1 << 29)) return GDPA_ERR_BAD_ARG;
   if (p->head_dim != 64 && p->head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM;
   if (p->q_offsets == nullptr || p->kv_offsets == nullptr || p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
   // TMA coordinates are 32-bit row indices.
@@ -239,6 +240,7 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.kv_heads = kv_heads;
   l.args.kv_group = p->heads / kv_heads;
   l.args.kv_index = p->kv_seq_index;
+  l.args.window = p->window_plus_one > 0 ? p->window_plus_one - 1 : -1;
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -322,6 +324,7 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.heads = kv_heads;
   l.args.q_heads = p->heads;
   l.args.kv_group = p->heads / kv_heads;
+  l.args.window = p->window_plus_one > 0 ? p->window_plus_one - 1 : -1;
   l.args.max_q = p->max_seq_len_q;
   l.args.max_kv = p->max_seq_len_kv;
   l.args.scale = p->qk_scale;

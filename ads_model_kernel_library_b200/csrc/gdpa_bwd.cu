@@ -164,8 +164,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int idx;
         while (walker.next(idx)) {
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-          const int nq1 = (w.lq + kTile - 1) / kTile;  // Q tiles of one query head
-          const int nq = nq1 * a.kv_group;             // ... of every query head of this K / V head's group
+          int m0, nq1;  // first Q tile and number of Q tiles of one query head this item visits
+          bwd_q_range(w, a.window, m0, nq1);
+          const int nq = nq1 * a.kv_group;  // ... over every query head of this K / V head's group
           if (nq == 0) continue;
           const int kv_row = static_cast<int>(w.kv_start) + w.blk * kTile;
           const int q_row = static_cast<int>(w.q_start);
@@ -182,7 +183,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v, bar, hf * 64, w.h, kv_row);
           }
           for (int m = 0; m < nq; ++m) {
-            const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
+            const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
             GDPA_WAIT(BB_Q_EMPTY + st, q_phase[st] ^ 1u, ST_ROLE_LOAD);
             q_phase[st] ^= 1u;
             {
@@ -226,7 +227,9 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int idx;
         while (walker.next(idx)) {
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-          const int nq = ((w.lq + kTile - 1) / kTile) * a.kv_group;
+          int m0, nq1;
+          bwd_q_range(w, a.window, m0, nq1);
+          const int nq = nq1 * a.kv_group;
           if (nq == 0) continue;
           GDPA_WAIT(BB_KV_FULL, kv_phase, ST_ROLE_MMA);
           kv_phase ^= 1u;
@@ -322,7 +325,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-      const int nq1 = (w.lq + kTile - 1) / kTile;
+      int m0, nq1;
+      bwd_q_range(w, a.window, m0, nq1);
       const int nq = nq1 * a.kv_group;
       const int kv_local = w.blk * kTile + row;
       const bool row_valid = kv_local < w.lkv;
@@ -338,11 +342,18 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         continue;
       }
-      const bool tile_rows_full = (w.blk + 1) * kTile <= w.lkv;
       for (int m = 0; m < nq; ++m) {
-        const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
-        const int qv = min(kTile, w.lq - mm * kTile);  // valid Q columns of this tile
-        const bool full = tile_rows_full && qv == kTile;
+        const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
+        // columns [clo, chi) of the tile take part for this thread's KV row: inside the Q length, the KV
+        // row inside the KV length, and inside the band
+        int clo = 0, chi = row_valid ? min(kTile, w.lq - mm * kTile) : 0;
+        if (a.window >= 0) {
+          clo = max(clo, kv_local - a.window - mm * kTile);
+          chi = min(chi, kv_local + a.window - mm * kTile + 1);
+        }
+        // the unmasked path is taken by the warp as a whole; without a band the test needs no vote
+        const bool full = (a.window < 0) ? ((w.blk + 1) * kTile <= w.lkv && w.lq - mm * kTile >= kTile)
+                                         : __all_sync(0xffffffffu, clo <= 0 && chi >= kTile);
         uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
         uint32_t ra[32], rb[32];
         if (tracer) GDPA_TRACE(a, tr * 32 + 8);
@@ -384,8 +395,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               const float2 l2 = *reinterpret_cast<const float2*>(stat_lse + col);
               float p0 = ex2_approx(fmaf(__uint_as_float(cur[2 * i]), c2, -l2.x));
               float p1 = ex2_approx(fmaf(__uint_as_float(cur[2 * i + 1]), c2, -l2.y));
-              p0 = (row_valid && col < qv) ? p0 : 0.f;
-              p1 = (row_valid && col + 1 < qv) ? p1 : 0.f;
+              p0 = (col >= clo && col < chi) ? p0 : 0.f;
+              p1 = (col + 1 >= clo && col + 1 < chi) ? p1 : 0.f;
               pk[i] = pack_bf16x2(p0, p1);
               g2[c * 16 + i] = pack_f32x2(p0, p1);
             }
@@ -394,12 +405,21 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int i = 0; i < 16; ++i)
               act_and_grad_pair<ACT, false>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
                                             true, true, pk[i], g2[c * 16 + i]);
-          } else {
+          } else if (a.window < 0) {
+            // edge tile without a band: the column bound is the same for every thread (cheap predicates)
+            const int qv = min(kTile, w.lq - mm * kTile);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int col = half * 64 + c * 32 + 2 * i;
               act_and_grad_pair<ACT, true>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
                                            row_valid && (col < qv), row_valid && (col + 1 < qv), pk[i], g2[c * 16 + i]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = half * 64 + c * 32 + 2 * i;
+              act_and_grad_pair<ACT, true>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
+                                           col >= clo && col < chi, col + 1 >= clo && col + 1 < chi, pk[i], g2[c * 16 + i]);
             }
           }
           // P^T chunk c of this half goes over columns this half has already read
@@ -501,10 +521,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
-      const int nq1 = (w.lq + kTile - 1) / kTile;
+      int m0, nq1;
+      bwd_q_range(w, a.window, m0, nq1);
       const int nq = nq1 * a.kv_group;
       for (int m = 0; m < nq; ++m) {
-        const int hq = w.h * a.kv_group + m / nq1, mm = m % nq1;
+        const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
         const int q_row0 = static_cast<int>(w.q_start) + mm * kTile + warp * 32;
         uint32_t r[D / 32][32];
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 13);

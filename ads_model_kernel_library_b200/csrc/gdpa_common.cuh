@@ -80,6 +80,40 @@ __device__ __forceinline__ Work load_work(const int* sched, int idx, const void*
   return w;
 }
 
+// Banded attention (the reference's window_size): a pair (q, kv) of sequence-local positions takes part
+// only if |q - kv| <= window; window < 0 means no band.  A forward work item (256 Q rows) then visits
+// only the KV tiles that can hold such a pair, a backward work item (128 KV rows) only such Q tiles.
+__device__ __forceinline__ void fwd_kv_range(const Work& w, int window, int& first, int& count) {
+  const int nkv = (w.lkv + kTile - 1) / kTile;
+  first = 0;
+  count = nkv;
+  if (window >= 0 && nkv > 0) {
+    const int q_lo = w.blk * kFwdQBlock;
+    const int q_hi = min(w.lq, q_lo + kFwdQBlock) - 1;
+    const int lo = max(0, q_lo - window) / kTile;
+    const int hi = min(nkv, (q_hi + window) / kTile + 1);
+    first = lo < hi ? lo : 0;
+    count = lo < hi ? hi - lo : 0;
+  }
+}
+__device__ __forceinline__ void bwd_q_range(const Work& w, int window, int& first, int& count) {
+  const int nq = (w.lq + kTile - 1) / kTile;
+  first = 0;
+  count = nq;
+  if (window >= 0 && nq > 0) {
+    const int kv_lo = w.blk * kTile;
+    const int kv_hi = min(w.lkv, kv_lo + kTile) - 1;
+    const int lo = max(0, kv_lo - window) / kTile;
+    const int hi = min(nq, (kv_hi + window) / kTile + 1);
+    first = lo < hi ? lo : 0;
+    count = lo < hi ? hi - lo : 0;
+  }
+}
+__device__ __forceinline__ bool in_window(int q_pos, int kv_pos, int window) {
+  const int d = q_pos - kv_pos;
+  return window < 0 || (d <= window && -d <= window);
+}
+
 // Persistent CTAs walk the longest-first list in a zigzag: round r gives CTA c the item
 // r*G + c on even rounds and r*G + (G-1-c) on odd rounds, so the CTA that drew the longest item of
 // one round draws the shortest of the next.

@@ -148,12 +148,13 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       int idx;
       while (walker.next(idx)) {
         const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
-        const int nkv = (w.lkv + kTile - 1) / kTile;
+        int j0, nkv;  // first KV tile and number of KV tiles this item visits
+        fwd_kv_range(w, a.window, j0, nkv);
         if (nkv == 0) continue;
         const int q0 = w.blk * kFwdQBlock;
         const int nst = (w.lq - q0 > kTile) ? 2 : 1;
         const int q_row = static_cast<int>(w.q_start) + q0;
-        const int kv_row = static_cast<int>(w.kv_start);
+        const int kv_row = static_cast<int>(w.kv_start) + j0 * kTile;
         // Issue order Q0, K0, Q1, V0, K1, V1, ...
         for (int step = 0; step < 2 * nkv + 2; ++step) {
           if (step == 0 || step == 2) {
@@ -226,7 +227,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       int idx;
       while (walker.next(idx)) {
         const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
-        const int nkv = (w.lkv + kTile - 1) / kTile;
+        int j0, nkv;
+        fwd_kv_range(w, a.window, j0, nkv);
         if (nkv == 0) continue;
         const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
         // First S tiles: S_s = Q_s K_0^T.
@@ -297,7 +299,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int idx;
     while (walker.next(idx)) {
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, a.kv_index);
-      const int nkv = (w.lkv + kTile - 1) / kTile;
+      int j0, nkv;
+      fwd_kv_range(w, a.window, j0, nkv);
       const int q0 = w.blk * kFwdQBlock;
       const int nst = (w.lq - q0 > kTile) ? 2 : 1;
       if (s >= nst) continue;
@@ -332,11 +335,17 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           kv_blk0 = load_offset(a.kv_blk_off, a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, w.b, a.off64)) : w.b, a.off64);
         }
         for (int j = 0; j < nkv; ++j) {
-          const int valid = min(kTile, w.lkv - j * kTile) - half * 64;
+          // columns [clo, chi) of this warp's 64 take part: inside the KV length and inside the band
+          const int kbase = (j0 + j) * kTile + half * 64;
+          int clo = 0, chi = min(kTile, w.lkv - (j0 + j) * kTile) - half * 64;
+          if (a.window >= 0) {
+            clo = max(clo, qr - a.window - kbase);
+            chi = min(chi, qr + a.window - kbase + 1);
+          }
           float c = a.scale * kLog2e, bias = 0.f, inv_sv = 1.f;
           if constexpr (FP8) {
-            const float sk = a.k_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
-            const float sv = a.v_scales[(kv_blk0 + j) * a.kv_heads + w.h / a.kv_group];
+            const float sk = a.k_scales[(kv_blk0 + j0 + j) * a.kv_heads + w.h / a.kv_group];
+            const float sv = a.v_scales[(kv_blk0 + j0 + j) * a.kv_heads + w.h / a.kv_group];
             c *= sq * sk;
             bias = log2f(sv);
             inv_sv = 1.f / sv;
@@ -357,7 +366,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float t = __uint_as_float(cur[i]) * c;
-              pmax = (ch * 32 + i < valid) ? fmaxf(pmax, t) : pmax;
+              pmax = (ch * 32 + i >= clo && ch * 32 + i < chi) ? fmaxf(pmax, t) : pmax;
             }
           }
           float* slot = rowmax + (((s_phase * 2 + s) * 2) * kTile);
@@ -370,7 +379,8 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (j == 0) {
             m_used = m_new;
           } else if (__any_sync(0xffffffffu, m_new > m_used + kThr)) {
-            const float alpha = ex2_approx(m_used - m_new);
+            // a row that has not seen a key yet (both maxima -inf) keeps its zeros
+            const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_used - m_new);
             row_sum *= alpha;
             m_used = m_new;
 #pragma unroll
@@ -386,7 +396,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           // pass 2: reload the scores, P = exp2(c S + bias - m), partial row sum, quantise, store over
           // columns of this half that have been read
-          const float off = bias - m_used;
+          const float off = (m_used == -INFINITY) ? 0.f : bias - m_used;  // a row may have seen no column yet
           float psum = 0.f;
           tmem_ld32(s_tmem, ra);
 #pragma unroll
@@ -397,7 +407,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (ch == 0) tmem_ld32(s_tmem + 32, rb);
             auto prob = [&](int i) {
               const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
-              const float p = (ch * 32 + i < valid) ? e : 0.f;
+              const float p = (ch * 32 + i >= clo && ch * 32 + i < chi) ? e : 0.f;
               psum += p;
               return p;
             };
@@ -428,15 +438,23 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         rowsum[(s * 2 + half) * kTile + row] = row_sum * kPScale;
         mbar_arrive(bar_base + 8u * (B_L_FULL + s));
         GDPA_WAIT_WARP(B_L_FULL + s, o_phase, ST_ROLE_EPI);
-        inv_l = 1.f / (row_sum * kPScale + reinterpret_cast<volatile float*>(rowsum)[(s * 2 + (half ^ 1)) * kTile + row]);
+        const float l_total = row_sum * kPScale + reinterpret_cast<volatile float*>(rowsum)[(s * 2 + (half ^ 1)) * kTile + row];
+        inv_l = l_total > 0.f ? 1.f / l_total : 0.f;  // a row whose band holds no key gives zeros
         if constexpr (!FP8) {
-          // log-sum-exp of the scaled scores in base 2, for the softmax backward
+          // log-sum-exp of the scaled scores in base 2, for the softmax backward (+inf for a row without
+          // keys, which makes every P of that row zero there)
           if (half == 0 && row_valid && a.lse != nullptr)
-            a.lse[static_cast<long long>(w.h) * a.total_q + w.q_start + qr] = m_used - log2f(inv_l);
+            a.lse[static_cast<long long>(w.h) * a.total_q + w.q_start + qr] = l_total > 0.f ? m_used + log2f(l_total) : INFINITY;
         }
       }
       for (int j = 0; !kSoftmax && j < nkv; ++j) {
-        const int valid = min(kTile, w.lkv - j * kTile) - half * 64;  // valid columns among this warp's 64
+        // columns [clo, chi) of this warp's 64 take part: inside the KV length and inside the band
+        const int kbase = (j0 + j) * kTile + half * 64;
+        int clo = 0, chi = min(kTile, w.lkv - (j0 + j) * kTile) - half * 64;
+        if (a.window >= 0) {
+          clo = max(clo, qr - a.window - kbase);
+          chi = min(chi, qr + a.window - kbase + 1);
+        }
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
         GDPA_WAIT_WARP(B_S_FULL + s, s_phase, ST_ROLE_ACT);
         s_phase ^= 1u;
@@ -451,15 +469,17 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_wait_ld();
           tmem_regs_ready(cur);
           if (c == 0) tmem_ld32(s_tmem + 32, rb);
-          if (valid >= (c + 1) * 32) {
+          // the unmasked path is taken by the warp as a whole
+          if (__all_sync(0xffffffffu, clo <= c * 32 && chi >= (c + 1) * 32)) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               pk[i] = act_scaled_pair_bf16<ACT>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale);
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float x0 = (c * 32 + 2 * i < valid) ? __uint_as_float(cur[2 * i]) : 0.f;
-              const float x1 = (c * 32 + 2 * i + 1 < valid) ? __uint_as_float(cur[2 * i + 1]) : 0.f;
+              const int c0 = c * 32 + 2 * i;
+              const float x0 = (c0 >= clo && c0 < chi) ? __uint_as_float(cur[2 * i]) : 0.f;
+              const float x1 = (c0 + 1 >= clo && c0 + 1 < chi) ? __uint_as_float(cur[2 * i + 1]) : 0.f;
               pk[i] = act_scaled_pair_bf16<ACT>(x0, x1, scale, hscale);
             }
           }

@@ -37,6 +37,7 @@ struct FwdArgs {
   int kv_heads;      // K / V heads; query head h reads K / V head h / kv_group
   int kv_group;      // heads / kv_heads
   const void* kv_index;  // optional: sequence -> entry of the KV offsets (shared KV sequences)
+  int window;            // band |q - kv| <= window of sequence-local positions; -1 = none
 };
 
 struct FwdLaunch {
@@ -65,6 +66,7 @@ struct BwdArgs {
   long long total_q;
   int q_heads;         // query heads; `heads` above is the number of K / V heads (the work items' heads)
   int kv_group;        // q_heads / heads: a work item walks the Q tiles of every query head of its group
+  int window;          // band |q - kv| <= window of sequence-local positions; -1 = none
 };
 
 struct BwdLaunch {

@@ -84,7 +84,7 @@ class GdpaFwdParams(C.Structure):
         ("timing_stop_event", C.c_void_p),
         ("lse", C.c_void_p),
         ("kv_heads", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("window_plus_one", C.c_int32),
         ("kv_seq_index", C.c_void_p),
         ("q_strides", C.c_int64 * 2),
         ("k_strides", C.c_int64 * 2),
@@ -124,7 +124,7 @@ class GdpaBwdParams(C.Structure):
         ("lse", C.c_void_p),
         ("dpsum", C.c_void_p),
         ("kv_heads", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("window_plus_one", C.c_int32),
         ("q_strides", C.c_int64 * 2),
         ("k_strides", C.c_int64 * 2),
         ("v_strides", C.c_int64 * 2),

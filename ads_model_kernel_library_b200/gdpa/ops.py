@@ -166,6 +166,7 @@ def _gdpa_forward_op(
     max_seq_len_kv: int,
     qk_scale: float,
     activation: int,
+    window_size: int = -1,
 ) -> torch.Tensor:
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
     with torch.cuda.device(query.device):
@@ -176,13 +177,14 @@ def _gdpa_forward_op(
                                 max_seq_len_q, max_seq_len_kv)
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
+        p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
     return o
 
 
 @_gdpa_forward_op.register_fake
-def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, window_size=-1):
     return query.new_empty(query.shape)
 
 
@@ -200,6 +202,7 @@ def _gdpa_backward_op(
     activation: int,
     out: Optional[torch.Tensor] = None,
     lse: Optional[torch.Tensor] = None,
+    window_size: int = -1,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
     if activation == SOFTMAX_ID and (out is None or lse is None):
@@ -238,6 +241,7 @@ def _gdpa_backward_op(
         p.schedule = sched.data_ptr()
         p.dq_accum = dq_accum.data_ptr()
         p.status = _status_word(query.device).data_ptr()
+        p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         if activation == SOFTMAX_ID:
             dpsum = torch.empty(max(query.shape[0] * H, 1), dtype=torch.float32, device=query.device)
             out = out.contiguous()
@@ -249,22 +253,23 @@ def _gdpa_backward_op(
 
 @_gdpa_backward_op.register_fake
 def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, out=None,
-      lse=None):
+      lse=None, window_size=-1):
     return query.new_empty(query.shape), key.new_empty(key.shape), value.new_empty(value.shape)
 
 
 def _setup_context(ctx, inputs, output):
-    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, activation = inputs
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, activation, window_size = inputs
     ctx.save_for_backward(query, key, value, query_offset, key_offset)
-    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation = max_q, max_kv, qk_scale, activation
+    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation, ctx.window_size = max_q, max_kv, qk_scale, activation, window_size
 
 
 def _backward(ctx, do):
     query, key, value, query_offset, key_offset = ctx.saved_tensors
     dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
-        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation
+        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation,
+        None, None, ctx.window_size
     )
-    return dq, dk, dv, None, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None, None
 
 
 _gdpa_forward_op.register_autograd(_backward, setup_context=_setup_context)
@@ -280,6 +285,7 @@ def _gdpa_forward_softmax_op(
     max_seq_len_q: int,
     max_seq_len_kv: int,
     qk_scale: float,
+    window_size: int = -1,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Softmax forward that also returns the base-2 log-sum-exp ``[H, total_q]`` its backward needs."""
     batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
@@ -293,29 +299,31 @@ def _gdpa_forward_softmax_op(
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, SOFTMAX_ID, sched, _cabi.GDPA_DTYPE_BF16)
         p.lse = lse.data_ptr()
+        p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
     return o, lse
 
 
 @_gdpa_forward_softmax_op.register_fake
-def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale):
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, window_size=-1):
     return query.new_empty(query.shape), torch.empty((query.shape[1], query.shape[0]), dtype=torch.float32, device=query.device)
 
 
 def _softmax_setup_context(ctx, inputs, output):
-    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale = inputs
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, window_size = inputs
     o, lse = output
     ctx.save_for_backward(query, key, value, query_offset, key_offset, o, lse)
-    ctx.max_q, ctx.max_kv, ctx.qk_scale = max_q, max_kv, qk_scale
+    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.window_size = max_q, max_kv, qk_scale, window_size
 
 
 def _softmax_backward(ctx, do, dlse):
     query, key, value, query_offset, key_offset, o, lse = ctx.saved_tensors
     dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
-        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, SOFTMAX_ID, o, lse
+        do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, SOFTMAX_ID, o, lse,
+        ctx.window_size
     )
-    return dq, dk, dv, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None
 
 
 _gdpa_forward_softmax_op.register_autograd(_softmax_backward, setup_context=_softmax_setup_context)
@@ -467,7 +475,8 @@ def generalized_dot_product_attention(
     Scheduling knobs of the reference (``seq_index``, ``enable_persistent``, ``enable_tma``,
     ``enable_ws``, ``use_dq_atomic_add``, ``bwd_opt_tech``, ``allow_tf32``, ``total_num_objects``) are
     accepted and ignored: scheduling is internal.  ``ad_to_request_offset`` (one KV sequence index per Q
-    sequence, so that many Q sequences share one KV sequence) is supported for the forward only.  Every
+    sequence, so that many Q sequences share one KV sequence) is supported for the forward only;
+    ``window_size=W`` keeps only pairs of sequence-local positions with ``|q - kv| <= W``.  Every
     other non-default option raises, as the
     reference does for masks and causality (:3138-3139).
     """
@@ -477,7 +486,7 @@ def generalized_dot_product_attention(
         raise NotImplementedError("Causal unsupported")
     unsupported = {
         "attn_offset": attn_offset, "output_offset": output_offset,
-        "window_size": window_size, "ts_encoding_params": ts_encoding_params,
+        "ts_encoding_params": ts_encoding_params,
         "ts_event_request_even_params": ts_event_request_even_params,
         "ts_event_request_log_params": ts_event_request_log_params,
         "ts_adjacent_event_log_params": ts_adjacent_event_log_params,
@@ -512,7 +521,12 @@ def generalized_dot_product_attention(
         query = expect_contiguous(query)
         key = expect_contiguous(key)
         value = expect_contiguous(value)
+    window = -1 if window_size is None else int(window_size)
+    if window_size is not None and window < 0:
+        raise ValueError("window_size must be non-negative")
     if ad_to_request_offset is not None:
+        if window >= 0:
+            raise NotImplementedError("window_size together with ad_to_request_offset is not supported")
         return torch.ops.gdpa.generalized_dot_product_attention_shared_kv(
             query, key, value, query_offset, key_offset, ad_to_request_offset, int(max_seq_len_q), int(max_seq_len_kv),
             scale, act_id
@@ -520,10 +534,10 @@ def generalized_dot_product_attention(
     if act_id == SOFTMAX_ID:
         # the trainable softmax variant keeps the log-sum-exp of the forward for its backward
         return torch.ops.gdpa.generalized_dot_product_attention_softmax(
-            query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale
+            query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, window
         )[0]
     return torch.ops.gdpa.generalized_dot_product_attention(
-        query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id
+        query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id, window
     )
 
 

@@ -160,7 +160,11 @@ typedef struct GdpaFwdParams {
    * K / V head h / (heads / kv_heads)).  0 = same as heads.  K, V (and the FP8 K / V scales) are then
    * [total_kv, kv_heads, head_dim]. */
   int32_t kv_heads;
-  int32_t reserved0;
+  /* Banded attention, the reference's window_size
+   * (gdpa/triton/triton_generalized_dot_product_attention.py:209-211, :274-278): a pair of sequence-local
+   * positions (q, kv) takes part only if |q - kv| <= window_size; scores outside are treated as 0 before
+   * the activation (excluded from the softmax).  Stored as window_size + 1; 0 = no band. */
+  int32_t window_plus_one;
   /* Optional [batch] map from a Q sequence to its KV sequence, as in GdpaSchedParams (forward only). */
   const void* kv_seq_index;
   /* Strides of Q, K, V in elements: {between rows (tokens), between heads}; the head dimension is always
@@ -242,7 +246,7 @@ typedef struct GdpaBwdParams {
    * [total_kv, kv_heads, head_dim] and sum the contributions of the query heads of a group; the
    * schedule must have been built with heads = kv_heads. */
   int32_t kv_heads;
-  int32_t reserved0;
+  int32_t window_plus_one;    /* banded attention, as in GdpaFwdParams: window_size + 1, 0 = no band */
   /* Strides of Q, K, V in elements, as in GdpaFwdParams (0 = contiguous).  dO, dQ, dK, dV are contiguous. */
   int64_t q_strides[2];
   int64_t k_strides[2];

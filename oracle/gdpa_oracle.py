@@ -86,6 +86,7 @@ def gdpa_forward(
     activation: str = "raw",
     qk_scale: Optional[float] = None,
     p_dtype: Optional[torch.dtype] = None,
+    window_size: Optional[int] = None,
 ) -> torch.Tensor:
     """O[b] = (act(Q_b K_b^T) * qk_scale) V_b per sequence and head, in fp32.
 
@@ -120,12 +121,24 @@ def gdpa_forward(
             k_i = k_i.repeat_interleave(group, dim=0)
             v_i = v_i.repeat_interleave(group, dim=0)
         s = torch.matmul(q_i, k_i.transpose(-2, -1))
+        band = None
+        if window_size is not None:
+            # |q - kv| <= window_size on sequence-local positions; scores outside are zeroed before the
+            # activation (gdpa/triton/triton_generalized_dot_product_attention.py:274-278)
+            pos_q = torch.arange(qe - qs).view(-1, 1)
+            pos_k = torch.arange(ke - ks).view(1, -1)
+            band = (pos_q - pos_k).abs() <= int(window_size)
         if act is None:
             if ke > ks:
-                p = F.softmax(s * scale, dim=-1)
+                sc = s * scale
+                if band is not None:
+                    sc = sc.masked_fill(~band, float("-inf"))
+                p = torch.nan_to_num(F.softmax(sc, dim=-1), nan=0.0)  # a row without keys in its band gives zeros
             else:
                 p = s
         else:
+            if band is not None:
+                s = torch.where(band, s, torch.zeros_like(s))
             p = act(s) * scale
         if p_dtype is not None:
             p = p.to(p_dtype).to(torch.float32)
@@ -143,6 +156,7 @@ def gdpa_forward_backward(
     grad_out: torch.Tensor,
     activation: str = "raw",
     qk_scale: Optional[float] = None,
+    window_size: Optional[int] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(O, dQ, dK, dV) in fp32 by autograd over :func:`gdpa_forward`.
 
@@ -153,7 +167,7 @@ def gdpa_forward_backward(
     q = query.detach().to(torch.float32).clone().requires_grad_(True)
     k = key.detach().to(torch.float32).clone().requires_grad_(True)
     v = value.detach().to(torch.float32).clone().requires_grad_(True)
-    o = gdpa_forward(q, k, v, query_offset, key_offset, activation, qk_scale)
+    o = gdpa_forward(q, k, v, query_offset, key_offset, activation, qk_scale, window_size=window_size)
     o.backward(grad_out.to(torch.float32))
     zero = torch.zeros_like
     return (

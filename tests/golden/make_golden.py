@@ -18,8 +18,8 @@ symlink of that name makes them resolve.  Four things are recorded:
   forward op body (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335) and the backward
   op body (:3461-3788), executed on the CPU by Triton's interpreter (``TRITON_INTERPRET=1``, autotuning
   off), on a jagged batch with different Q and KV lengths and ``qk_scale = 0.25``, for every activation
-  of the table; plus one grouped-query case (4 query heads, 2 K/V heads).  These pin where the scale is
-  applied and every gradient;
+  of the table; plus one grouped-query case (4 query heads, 2 K/V heads) and one banded case
+  (``window_size = 6``).  These pin where the scale is applied and every gradient;
 * ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
 
 Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
@@ -136,6 +136,14 @@ def main(ref_root: str) -> None:
                activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
     out.update(gqa_q=qg.numpy(), gqa_k=kg.numpy(), gqa_v=vg.numpy(), gqa_do=dog.numpy(), gqa_o=og.numpy(),
                gqa_dq=resg[0].numpy(), gqa_dk=resg[1].numpy(), gqa_dv=resg[2].numpy())
+
+    # banded attention: |q - kv| <= window_size
+    W = 6
+    ow = fwd(q, k, v, qo, ko, int(lq.max()), int(lk.max()), qk_scale=scale, window_size=W, activation="gelu_approx")
+    resw = bwd(do, q, k, v, ow, qo, ko, B, H, 1, int(lq.max()), int(lk.max()), D, D, qk_scale=scale, window_size=W,
+               activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
+    out.update(window_size=np.int32(W), window_o=ow.numpy(), window_dq=resw[0].numpy(), window_dk=resw[1].numpy(),
+               window_dv=resw[2].numpy())
 
     np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
     ids = {a.value: i for a, i in ref_math.activation_to_int.items()}

@@ -347,3 +347,28 @@ def test_fused_qkv_and_fused_kv_layouts(G):
     assert_close(o, ro, "O[fused KV]")
     assert_close(xq.grad, rdq, "dQ[fused KV]")
     assert_close(xkv.grad, torch.cat([rdk, rdv], dim=-1), "d(KV)")
+
+
+@pytest.mark.parametrize("act", ["gelu_approx", "softmax"])
+@pytest.mark.parametrize("window", [0, 37, 200, 5000])
+def test_banded_attention_window_size(G, act, window):
+    """window_size = W keeps only pairs of sequence-local positions with |q - kv| <= W, forward and
+    backward; a window wider than every sequence changes nothing."""
+    lq, lk = [300, 70, 513, 129], [260, 200, 700, 131]
+    cpu, dev = jagged_inputs(lq, lk, 2, 128, seed=61, std=0.5)
+    from oracle import gdpa_oracle as orc
+
+    q, k, v = (dev[n].clone().requires_grad_(True) for n in ("q", "k", "v"))
+    o = G.generalized_dot_product_attention(q, k, v, dev["qo"], dev["ko"], max(lq), max(lk), qk_scale=0.1, activation=act,
+                                            window_size=window)
+    o.backward(dev["do"])
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    ro, rdq, rdk, rdv = orc.gdpa_forward_backward(cpu["q"].float(), cpu["k"].float(), cpu["v"].float(), cpu["qo"], cpu["ko"],
+                                                  cpu["do"].float(), act, 0.1, window_size=window)
+    for a, b, n in ((o, ro, "O"), (q.grad, rdq, "dQ"), (k.grad, rdk, "dK"), (v.grad, rdv, "dV")):
+        assert_close(a, b, f"{n}[{act}, window {window}]")
+    if window == 5000:
+        o2 = G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], max(lq), max(lk),
+                                                 qk_scale=0.1, activation=act)
+        assert torch.equal(o2, o)

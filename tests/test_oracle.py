@@ -101,3 +101,13 @@ def test_oracle_matches_reference_triton_kernels_grouped_query(golden):
                                               "gelu_approx", float(golden["triton_scale"]))
     for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
         torch.testing.assert_close(got, t(f"gqa_{name}"), atol=2e-5, rtol=2e-5)
+
+
+def test_oracle_matches_reference_triton_kernels_banded(golden):
+    """window_size: pairs with |q - kv| > W are zeroed before the activation, forward and backward."""
+    t = lambda n: torch.from_numpy(golden[n])
+    o, dq, dk, dv = orc.gdpa_forward_backward(t("triton_q"), t("triton_k"), t("triton_v"), t("triton_qo"), t("triton_ko"),
+                                              t("triton_do"), "gelu_approx", float(golden["triton_scale"]),
+                                              window_size=int(golden["window_size"]))
+    for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        torch.testing.assert_close(got, t(f"window_{name}"), atol=2e-5, rtol=2e-5)
