@@ -2,9 +2,11 @@
 // with S and P recomputed (nothing but Q, K, V, dO is read).
 //
 // One persistent CTA per SM walks a longest-first list of work items (sequence, head, 128-row KV
-// tile).  The item's K and V tiles stay resident in shared memory; Q and dO tiles of the sequence
-// stream through two-stage rings.  Per Q tile m the tensor cores run five contractions, with the KV
-// rows as the M dimension of the "transposed" score tiles:
+// tile).  The item's K and V tiles stay resident in shared memory; the Q tiles of the sequence stream
+// through a two-stage ring, the dO tiles through one stage (with grouped-query attention the item walks
+// the Q tiles of every query head of its group; with a band only the Q tiles the band can reach).
+// Per Q tile m the tensor cores run five contractions, with the KV rows as the M dimension of the
+// "transposed" score tiles:
 //
 //   S^T  = K Q_m^T          (smem x smem)        -> TMEM [0,128)
 //   dP^T = V dO_m^T         (smem x smem)        -> TMEM [128,256)
@@ -15,13 +17,16 @@
 // issued in the order S(m), dK(m-1), dQ(m-1), dP(m), dV(m) (dK reads dS^T from TMEM, where it sits
 // over the dP^T columns that dQ then overwrites) so that the element-wise work of tile m
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
-// dQ tiles are drained by a dedicated warpgroup into shared memory and added into an fp32
-// accumulator by TMA reduce-add (32-column slabs, two staging buffers); a second kernel rounds the
-// accumulator to bf16.  Q rows of a tile beyond the sequence carry dS = 0, so what the reduce adds to
+// dQ tiles are drained by a dedicated warpgroup (whole tile into registers, TMEM released, then each
+// warp stages its 32 rows in shared memory) and added into an fp32 accumulator by TMA reduce-add; a
+// second kernel rounds the accumulator to bf16.  Q rows of a tile beyond the sequence carry dS = 0, so what the reduce adds to
 // the rows of the next sequence is exactly zero; rows beyond the tensor are clipped by the TMA unit.
 //
-// Roles (16 warps): warps 0-3 dQ reduce, warps 4-11 element-wise (warp w: TMEM lanes 32*(w%4),
-// score columns 64*((w-4)/4)), warp 12 MMA issuer, warp 13 TMA loader, warps 14-15 idle.
+// Softmax: P^T = 2^(c S^T - lse[q]) from the forward's log-sum-exp and dS = scale P (dP - dPsum[q]); the
+// per-column statistics of a Q tile reach the element-wise warps through shared memory.
+//
+// Roles (16 warps, setmaxnreg 144 / 144 / 80): warps 0-3 dQ reduce, warps 4-11 element-wise (warp w:
+// TMEM lanes 32*(w%4), score columns 64*((w-4)/4)), warp 12 MMA issuer, warp 13 TMA loader, warps 14-15 idle.
 // P^T of column half h is written over the first 32 columns of that half's own S^T columns
 // ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
