@@ -200,6 +200,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
     return GDPA_ERR_BAD_ARG;
   const int kv_heads = p->kv_heads > 0 ? p->kv_heads : p->heads;
   if (p->heads % kv_heads != 0) return GDPA_ERR_BAD_ARG;
+  if ((p->residual != nullptr || p->row_sumsq != nullptr) && (fp8 || act == ACT_SOFTMAX)) return GDPA_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(p->residual) & 15u) != 0) return GDPA_ERR_MISALIGNED;
   DeviceInfo di;
   rc = device_info(&di);
   if (rc != GDPA_OK) return rc;
@@ -241,6 +243,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.kv_group = p->heads / kv_heads;
   l.args.kv_index = p->kv_seq_index;
   l.args.window = p->window_plus_one > 0 ? p->window_plus_one - 1 : -1;
+  l.args.residual = static_cast<const __nv_bfloat16*>(p->residual);
+  l.args.row_sumsq = p->row_sumsq;
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -264,6 +268,48 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
 int gdpa_fwd(const GdpaFwdParams* p, gdpa_stream_t stream) { return fwd_common(p, stream, false); }
 
 int gdpa_fwd_fp8(const GdpaFwdParams* p, gdpa_stream_t stream) { return fwd_common(p, stream, true); }
+
+static int norm_args(const GdpaNormParams* p, NormArgs* a) {
+  if (p == nullptr || p->struct_size != sizeof(GdpaNormParams)) return GDPA_ERR_BAD_ARG;
+  if (p->rows < 0 || p->n <= 0 || p->n % 8 != 0 || !(p->eps >= 0.f)) return GDPA_ERR_BAD_ARG;
+  if (p->rows > 0 && (p->x == nullptr || p->out == nullptr)) return GDPA_ERR_BAD_ARG;
+  if ((p->row_mean == nullptr) != (p->row_rstd == nullptr) && p->row_mean != nullptr) return GDPA_ERR_BAD_ARG;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->out) |
+                          reinterpret_cast<uintptr_t>(p->residual) | reinterpret_cast<uintptr_t>(p->weight) |
+                          reinterpret_cast<uintptr_t>(p->bias);
+  if ((align & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  a->x = static_cast<const __nv_bfloat16*>(p->x);
+  a->out = static_cast<__nv_bfloat16*>(p->out);
+  a->weight = p->weight;
+  a->bias = p->bias;
+  a->residual = static_cast<const __nv_bfloat16*>(p->residual);
+  a->row_sumsq = p->row_sumsq;
+  a->row_mean = p->row_mean;
+  a->row_rstd = p->row_rstd;
+  a->rows = p->rows;
+  a->n = p->n;
+  a->eps = p->eps;
+  return GDPA_OK;
+}
+
+int gdpa_layernorm_rows(const GdpaNormParams* p, gdpa_stream_t stream) {
+  NormArgs a;
+  int rc = norm_args(p, &a);
+  if (rc != GDPA_OK) return rc;
+  if (a.row_mean == nullptr) a.row_rstd = nullptr;
+  rc = launch_layernorm_rows(a, static_cast<cudaStream_t>(stream));
+  if (rc == 0 && a.rows > 0) g_launches.fetch_add(1);
+  return rc;
+}
+
+int gdpa_rmsnorm_rows(const GdpaNormParams* p, gdpa_stream_t stream) {
+  NormArgs a;
+  int rc = norm_args(p, &a);
+  if (rc != GDPA_OK) return rc;
+  rc = launch_rmsnorm_rows(a, static_cast<cudaStream_t>(stream));
+  if (rc == 0 && a.rows > 0) g_launches.fetch_add(1);
+  return rc;
+}
 
 int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   int rc = check_common(p);

@@ -164,10 +164,10 @@ __device__ __forceinline__ float act_scaled(float x, float scale, float hscale) 
 
 // Two activations at once, packed bf16x2 result (x0 in the low half).  GELU-tanh and SiLU use packed
 // f32x2 arithmetic around the two MUFU evaluations; the other classes fall back to the scalar form.
-// Measured on B200: tanh.approx.f32 issues at half the rate of ex2 / rcp (16 cycles per warp
-// instruction and SM sub-partition), the two-value tanh.approx.f16x2 is no faster per element, and
-// sigmoid built from ex2 plus a Newton reciprocal on the FMA pipe costs more issue slots than it saves
-// MUFU cycles; the plain f32 tanh below was the fastest of the three.
+// Measured on B200: tanh.approx.f32 and ex2.approx both issue at 8 cycles per warp instruction and SM
+// sub-partition, the two-value tanh.approx.f16x2 at 16 (no faster per element), fma.rn.f32x2 at 2 (it saves
+// issue slots, not FMA-pipe cycles), and sigmoid built from ex2 plus a Newton reciprocal costs more issue
+// slots than it saves; the plain f32 tanh below was the fastest of the three.
 template <int ACT>
 __device__ __forceinline__ uint32_t act_scaled_pair_bf16(float x0, float x1, float scale, float hscale) {
   if constexpr (ACT == ACT_GELU_TANH) {

@@ -82,6 +82,18 @@ struct FwdSmem {
     if (!__all_sync(0xffffffffu, ok_)) goto role_done;                                                              \
   }
 
+// Sum of squares of eight bf16 values packed in a uint4.
+__device__ __forceinline__ float sumsq_bf16x8(const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+    s = fmaf(lo, lo, fmaf(hi, hi, s));
+  }
+  return s;
+}
+
 template <int D, int ACT, bool FP8>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -306,11 +318,26 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (s >= nst) continue;
       const int qr = q0 + s * kTile + row;
       const bool row_valid = qr < w.lq;
-      uint4* dst = reinterpret_cast<uint4*>(a.o + ((w.q_start + qr) * a.heads + w.h) * static_cast<long long>(D) + half * (D / 2));
+      const long long o_elem = ((w.q_start + qr) * a.heads + w.h) * static_cast<long long>(D) + half * (D / 2);
+      uint4* dst = reinterpret_cast<uint4*>(a.o + o_elem);
+      // fused epilogue of the norm pipeline: x = O + residual, and the sum of x^2 over this thread's half row is
+      // added to the row's entry of row_sumsq (the RMS norm over all heads is finished by a second kernel)
+      // (compiled out of the softmax instantiations, which have no registers to spare)
+      const uint4* res = (!kSoftmax && a.residual != nullptr) ? reinterpret_cast<const uint4*>(a.residual + o_elem) : nullptr;
+      float* const row_sumsq = kSoftmax ? nullptr : a.row_sumsq;
+      float ssq = 0.f;
       if (nkv == 0) {
         if (row_valid) {
 #pragma unroll
-          for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          for (int i = 0; i < D / 16; ++i) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (res != nullptr) {
+              v = res[i];
+              ssq += sumsq_bf16x8(v);
+            }
+            dst[i] = v;
+          }
+          if (row_sumsq != nullptr) atomicAdd(row_sumsq + w.q_start + qr, ssq);
         }
         continue;
       }
@@ -507,17 +534,36 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
         }
         if (row_valid) {
+          if (kSoftmax || (res == nullptr && row_sumsq == nullptr)) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv_l, __uint_as_float(r[8 * i + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv_l, __uint_as_float(r[8 * i + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv_l, __uint_as_float(r[8 * i + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv_l, __uint_as_float(r[8 * i + 7]) * inv_l);
-            dst[c * 4 + i] = v;
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv_l, __uint_as_float(r[8 * i + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv_l, __uint_as_float(r[8 * i + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv_l, __uint_as_float(r[8 * i + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv_l, __uint_as_float(r[8 * i + 7]) * inv_l);
+              dst[c * 4 + i] = v;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 rv = make_uint4(0, 0, 0, 0);
+              if (res != nullptr) rv = res[c * 4 + i];
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+              uint32_t ow[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float x0 = fmaf(__uint_as_float(r[8 * i + 2 * j]), inv_l, __uint_as_float(rw[j] << 16));
+                const float x1 = fmaf(__uint_as_float(r[8 * i + 2 * j + 1]), inv_l, __uint_as_float(rw[j] & 0xffff0000u));
+                ssq = fmaf(x0, x0, fmaf(x1, x1, ssq));
+                ow[j] = pack_bf16x2(x0, x1);
+              }
+              dst[c * 4 + i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
           }
         }
       }
+      if (row_sumsq != nullptr && row_valid) atomicAdd(row_sumsq + w.q_start + qr, ssq);
     }
   }
 

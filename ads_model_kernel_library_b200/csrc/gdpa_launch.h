@@ -38,6 +38,24 @@ struct FwdArgs {
   int kv_group;      // heads / kv_heads
   const void* kv_index;  // optional: sequence -> entry of the KV offsets (shared KV sequences)
   int window;            // band |q - kv| <= window of sequence-local positions; -1 = none
+  // norm pipeline: optional [total_q, heads, D] bf16 tensor added to O before it is stored, and optional
+  // [total_q] fp32 array that receives the sum over heads and columns of the squares of what is stored
+  const __nv_bfloat16* residual;
+  float* row_sumsq;
+};
+
+struct NormArgs {
+  const __nv_bfloat16* x;
+  __nv_bfloat16* out;
+  const float* weight;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  const float* row_sumsq;
+  float* row_mean;
+  float* row_rstd;
+  long long rows;
+  int n;
+  float eps;
 };
 
 struct FwdLaunch {
@@ -97,6 +115,8 @@ int launch_bwd_bf16(const BwdLaunch& l, int head_dim, int act_class);
 int launch_dpsum(const __nv_bfloat16* d_o, const __nv_bfloat16* o, float* dpsum, long long total_q, int heads, int head_dim,
                  cudaStream_t stream);
 int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
+int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream);
+int launch_rmsnorm_rows(const NormArgs& a, cudaStream_t stream);
 int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
 
 }  // namespace gdpa

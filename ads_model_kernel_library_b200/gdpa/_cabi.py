@@ -25,6 +25,8 @@ EXPORTS = (
     "gdpa_fwd",
     "gdpa_fwd_fp8",
     "gdpa_fwd_noalloc",
+    "gdpa_layernorm_rows",
+    "gdpa_rmsnorm_rows",
     "gdpa_bwd_workspace_bytes",
     "gdpa_bwd",
     "gdpa_strerror",
@@ -89,6 +91,26 @@ class GdpaFwdParams(C.Structure):
         ("q_strides", C.c_int64 * 2),
         ("k_strides", C.c_int64 * 2),
         ("v_strides", C.c_int64 * 2),
+        ("residual", C.c_void_p),
+        ("row_sumsq", C.c_void_p),
+    ]
+
+
+class GdpaNormParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("n", C.c_int32),
+        ("rows", C.c_int64),
+        ("x", C.c_void_p),
+        ("out", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("residual", C.c_void_p),
+        ("row_sumsq", C.c_void_p),
+        ("row_mean", C.c_void_p),
+        ("row_rstd", C.c_void_p),
+        ("eps", C.c_float),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -146,6 +168,9 @@ def _load() -> C.CDLL:
     lib.gdpa_fwd.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
     lib.gdpa_fwd_noalloc.restype = C.c_int
     lib.gdpa_fwd_noalloc.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
+    for fn in (lib.gdpa_layernorm_rows, lib.gdpa_rmsnorm_rows):
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(GdpaNormParams), C.c_void_p]
     lib.gdpa_fwd_fp8.restype = C.c_int
     lib.gdpa_fwd_fp8.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
     lib.gdpa_bwd_workspace_bytes.restype = C.c_size_t

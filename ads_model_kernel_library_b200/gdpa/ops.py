@@ -15,7 +15,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from . import _cabi
-from .math import SOFTMAX_ID, activation_string_to_int
+from .math import SOFTMAX_ID, activation_string_to_int, int_to_activation
 
 _SUPPORTED_HEAD_DIMS = (64, 128)
 _status_words = {}
@@ -476,16 +476,17 @@ def generalized_dot_product_attention(
     ``enable_ws``, ``use_dq_atomic_add``, ``bwd_opt_tech``, ``allow_tf32``, ``total_num_objects``) are
     accepted and ignored: scheduling is internal.  ``ad_to_request_offset`` (one KV sequence index per Q
     sequence, so that many Q sequences share one KV sequence) is supported for the forward only;
-    ``window_size=W`` keeps only pairs of sequence-local positions with ``|q - kv| <= W``.  Every
-    other non-default option raises, as the
-    reference does for masks and causality (:3138-3139).
+    ``window_size=W`` keeps only pairs of sequence-local positions with ``|q - kv| <= W``;
+    ``broadcast_q`` (one Q sequence shared by the whole batch) and ``ensemble_activation_list`` (one
+    activation id per head) are composed on the host from calls of the same kernels.  Every other
+    non-default option raises, as the reference does for masks and causality (:3138-3139).
     """
     if attn_mask is not None:
         raise NotImplementedError("attn_mask/bias unsupported")
     if is_causal:
         raise NotImplementedError("Causal unsupported")
     unsupported = {
-        "attn_offset": attn_offset, "output_offset": output_offset,
+        "attn_offset": attn_offset,
         "ts_encoding_params": ts_encoding_params,
         "ts_event_request_even_params": ts_event_request_even_params,
         "ts_event_request_log_params": ts_event_request_log_params,
@@ -495,18 +496,21 @@ def generalized_dot_product_attention(
         "ts_event_request_log_bucket_values": ts_event_request_log_bucket_values,
         "ts_adjacent_event_log_bucket_values": ts_adjacent_event_log_bucket_values,
         "pos_emb_params": pos_emb_params, "pos_emb_bucket_values": pos_emb_bucket_values,
-        "ensemble_activation_list": ensemble_activation_list,
     }
     for name, val in unsupported.items():
         if val is not None:
             raise NotImplementedError(f"{name} is not supported by this implementation")
-    if use_start_end_offsets or broadcast_q:
-        raise NotImplementedError("use_start_end_offsets / broadcast_q are not supported by this implementation")
+    if use_start_end_offsets:
+        raise NotImplementedError("use_start_end_offsets is not supported by this implementation")
+    if output_offset is not None and not broadcast_q:
+        raise NotImplementedError("output_offset is supported together with broadcast_q only")
     act_id = activation_string_to_int(activation)
     scale = 1.0 if qk_scale is None else float(qk_scale)
     # Packed layouts of the reference (:605-622): query = [T, H, 3D] with key = value = None, or
     # key = [T, H, 2D] with value = None.  The slices are strided views the kernels read in place.
     if key is None and value is None:
+        if broadcast_q:  # the reference asserts the same (:3143-3145 for offsets, :606 for the layout)
+            raise ValueError("broadcast_q cannot be combined with a fused QKV tensor")
         if query.shape[-1] % 3 != 0:
             raise ValueError("a fused QKV tensor must have a last dimension of 3 * head_dim")
         query, key, value = expect_contiguous(query).split(query.shape[-1] // 3, dim=-1)
@@ -524,6 +528,15 @@ def generalized_dot_product_attention(
     window = -1 if window_size is None else int(window_size)
     if window_size is not None and window < 0:
         raise ValueError("window_size must be non-negative")
+    if broadcast_q:
+        if ad_to_request_offset is not None:
+            raise NotImplementedError("broadcast_q together with ad_to_request_offset is not supported")
+        query, query_offset = _broadcast_query(query, query_offset, key_offset, output_offset)
+    if ensemble_activation_list:
+        if ad_to_request_offset is not None:
+            raise NotImplementedError("ensemble_activation_list together with ad_to_request_offset is not supported")
+        return _ensemble(query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale,
+                         act_id, window, [int(a) for a in ensemble_activation_list])
     if ad_to_request_offset is not None:
         if window >= 0:
             raise NotImplementedError("window_size together with ad_to_request_offset is not supported")
@@ -531,14 +544,74 @@ def generalized_dot_product_attention(
             query, key, value, query_offset, key_offset, ad_to_request_offset, int(max_seq_len_q), int(max_seq_len_kv),
             scale, act_id
         )
+    return _dispatch(query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id,
+                     window)
+
+
+def _dispatch(query, key, value, query_offset, key_offset, max_q: int, max_kv: int, scale: float, act_id: int,
+              window: int) -> torch.Tensor:
     if act_id == SOFTMAX_ID:
         # the trainable softmax variant keeps the log-sum-exp of the forward for its backward
         return torch.ops.gdpa.generalized_dot_product_attention_softmax(
-            query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, window
+            query, key, value, query_offset, key_offset, max_q, max_kv, scale, window
         )[0]
     return torch.ops.gdpa.generalized_dot_product_attention(
-        query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id, window
+        query, key, value, query_offset, key_offset, max_q, max_kv, scale, act_id, window
     )
+
+
+def _broadcast_query(query, query_offset, key_offset, output_offset):
+    """``broadcast_q`` of the reference (:949-952, :3028, :3088-3089): ``query`` holds ONE sequence
+    (``query_offset = [0, Lq]``) that every KV sequence of the batch attends with; the output is
+    ``[B * Lq, H, D]`` with the rows of batch element z at ``output_offset[z]``, and dQ is the sum over the
+    batch.  Composed on the host: the Q rows are repeated B times (a tensor of the size of the output) and
+    the ordinary operator runs on them, so autograd sums dQ over the batch.  ``output_offset`` must be the
+    dense layout ``[0, Lq, 2 Lq, ...]`` (the only one that fills the reference's output tensor); it is
+    built here when it is not given."""
+    if query_offset.numel() != 2:
+        raise ValueError("broadcast_q expects a single query sequence: query_offset = [0, Lq]")
+    batch = key_offset.numel() - 1
+    lq = query.shape[0]
+    if output_offset is None:
+        output_offset = torch.arange(batch + 1, device=query.device, dtype=key_offset.dtype) * lq
+    elif output_offset.numel() != batch + 1:
+        raise ValueError("output_offset must have one entry per KV sequence plus one")
+    return query.repeat(batch, 1, 1), output_offset.to(key_offset.dtype).contiguous()
+
+
+def _ensemble(query, key, value, query_offset, key_offset, max_q, max_kv, scale, act_id, window,
+              ensemble: List[int]) -> torch.Tensor:
+    """Per-head activations (the reference's ``ensemble_activation_list``, :958-961: head i < len(list)
+    uses activation id list[i], the other heads the base activation).  Composed on the host: heads are cut
+    into runs of equal activation (aligned to K/V heads under grouped-query attention), each run is one
+    call of the operator on strided head slices, and the outputs are concatenated along the head axis, so
+    autograd assembles the gradients."""
+    H, Hkv = query.shape[1], key.shape[1]
+    if Hkv < 1 or H % Hkv != 0:
+        raise ValueError("the number of query heads must be a multiple of the number of key/value heads")
+    G = H // Hkv
+    acts = [ensemble[h] if h < len(ensemble) else act_id for h in range(H)]
+    for a in set(acts):
+        if a != SOFTMAX_ID and a not in int_to_activation:
+            raise ValueError(f"Unsupported activation id: {a}")
+    # units of (first query head, last + 1, first K/V head, last + 1, activation): whole K/V heads whose
+    # query heads agree, else single query heads; neighbouring whole-head units of one activation merge
+    units = []
+    for kvh in range(Hkv):
+        lo, hi = kvh * G, (kvh + 1) * G
+        if len(set(acts[lo:hi])) == 1:
+            if units and units[-1][4] == acts[lo] and units[-1][1] == lo and units[-1][5]:
+                units[-1] = (units[-1][0], hi, units[-1][2], kvh + 1, acts[lo], True)
+            else:
+                units.append((lo, hi, kvh, kvh + 1, acts[lo], True))
+        else:
+            units.extend((h, h + 1, kvh, kvh + 1, acts[h], False) for h in range(lo, hi))
+    outs = [
+        _dispatch(query[:, lo:hi], key[:, klo:khi], value[:, klo:khi], query_offset, key_offset, max_q, max_kv, scale,
+                  act, window)
+        for lo, hi, klo, khi, act, _ in units
+    ]
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
 
 
 def quantize_fp8_blockwise(x: torch.Tensor, offsets: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:

@@ -175,6 +175,15 @@ typedef struct GdpaFwdParams {
   int64_t q_strides[2];
   int64_t k_strides[2];
   int64_t v_strides[2];
+  /* Fused epilogue of the norm pipeline (gdpa_fwd with an element-wise activation only; GDPA_ERR_BAD_ARG
+   * with softmax or FP8): when `residual` is set
+   * ([total_q, heads, head_dim] bf16, contiguous) the kernel stores O + residual instead of O (the
+   * reference's fused_q_residual_add, gdpa_megakernel/src/tlx_gdpa_megakernel.py:1076-1082); when
+   * `row_sumsq` is set ([total_q] fp32, zeroed by the caller) every row's sum over heads and columns of the
+   * squares of the stored values (taken before rounding to bf16) is added to it, which gdpa_rmsnorm_rows()
+   * then turns into the RMS norm over heads * head_dim (:359-405).  Null = plain O. */
+  const void* residual;
+  float* row_sumsq;
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
@@ -192,6 +201,33 @@ int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);
  *  - Calls no cudaMalloc / cudaFree and no allocating library routine. */
 #define GDPA_NOALLOC_MAX_ITEMS 65536
 int gdpa_fwd_noalloc(const GdpaFwdParams* params, gdpa_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Row norms either side of the forward, for the reference's GDPA-plus-norm pipeline
+ * (gdpa_megakernel/src/tlx_gdpa_megakernel.py:8155-8192: fused_layernorm, fused_q_residual_add,
+ * fused_rms_norm, fused_residual_add).  Rows are tokens, `n` = heads * head_dim bf16 values per row
+ * (a multiple of 8, rows contiguous and 16-byte aligned).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct GdpaNormParams {
+  uint32_t struct_size;   /* sizeof(GdpaNormParams) */
+  int32_t n;              /* values per row */
+  int64_t rows;
+  const void* x;          /* [rows, n] bf16 */
+  void* out;              /* [rows, n] bf16; may alias x */
+  const float* weight;    /* optional [n] fp32 */
+  const float* bias;      /* optional [n] fp32 (layer norm only) */
+  const void* residual;   /* optional [rows, n] bf16 added AFTER the RMS norm (fused_residual_add) */
+  const float* row_sumsq; /* RMS norm: optional [rows] fp32 sums of squares from gdpa_fwd; null = computed here */
+  float* row_mean;        /* optional [rows] fp32 outputs: layer-norm mean ...                    */
+  float* row_rstd;        /*   ... and 1 / sqrt(var + eps), or 1 / rms for the RMS norm            */
+  float eps;
+  int32_t reserved;
+} GdpaNormParams;
+
+/* out = (x - mean(x)) / sqrt(var(x) + eps) * weight + bias per row (biased variance, as torch layer_norm). */
+int gdpa_layernorm_rows(const GdpaNormParams* params, gdpa_stream_t stream);
+/* out = x / sqrt(mean(x^2) + eps) * weight + residual per row. */
+int gdpa_rmsnorm_rows(const GdpaNormParams* params, gdpa_stream_t stream);
 
 /* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule

@@ -178,6 +178,77 @@ def gdpa_forward_backward(
     )
 
 
+def gdpa_forward_ensemble(query, key, value, query_offset, key_offset, activations, qk_scale=None, window_size=None):
+    """Per-head activations: head h uses ``activations[h]`` (the reference's ensemble_activation_list,
+    gdpa/triton/triton_generalized_dot_product_attention.py:958-961, backward :2686-2688).  One
+    :func:`gdpa_forward` per query head, concatenated; differentiable."""
+    H, Hkv = query.shape[1], key.shape[1]
+    G = H // Hkv
+    outs = [
+        gdpa_forward(query[:, h:h + 1], key[:, h // G:h // G + 1], value[:, h // G:h // G + 1], query_offset, key_offset,
+                     activations[h], qk_scale, window_size=window_size)
+        for h in range(H)
+    ]
+    return torch.cat(outs, dim=1)
+
+
+def gdpa_forward_broadcast_q(query, key, value, key_offset, activation="raw", qk_scale=None):
+    """``broadcast_q``: the single Q sequence ``query`` ([Lq, H, D]) attends with every KV sequence of the batch;
+    output ``[B * Lq, H, D]`` with the rows of batch element z at z * Lq (off_q_z = 0 at
+    gdpa/triton/triton_generalized_dot_product_attention.py:949-952; output shape :3028).  Differentiable:
+    dQ sums over the batch, as the reference's atomic adds do (:2582-2583)."""
+    lq = query.shape[0]
+    qo = torch.tensor([0, lq])
+    outs = []
+    for z in range(key_offset.numel() - 1):
+        ks, ke = int(key_offset[z]), int(key_offset[z + 1])
+        outs.append(gdpa_forward(query, key[ks:ke], value[ks:ke], qo, torch.tensor([0, ke - ks]), activation, qk_scale))
+    return torch.cat(outs, dim=0)
+
+
+def forward_backward_of(fn, query, key, value, grad_out):
+    """(O, dQ, dK, dV) in fp32 by autograd over ``fn(q, k, v)``, for the composed variants above."""
+    q = query.detach().to(torch.float32).clone().requires_grad_(True)
+    k = key.detach().to(torch.float32).clone().requires_grad_(True)
+    v = value.detach().to(torch.float32).clone().requires_grad_(True)
+    o = fn(q, k, v)
+    o.backward(grad_out.to(torch.float32))
+    zero = torch.zeros_like
+    return (o.detach(), q.grad if q.grad is not None else zero(q), k.grad if k.grad is not None else zero(k),
+            v.grad if v.grad is not None else zero(v))
+
+
+def gdpa_with_norms(query, key, value, query_offset, key_offset, activation="fast_gelu", qk_scale=None,
+                    fused_layernorm=False, layernorm_weight=None, layernorm_bias=None, fused_q_residual_add=False,
+                    fused_rms_norm=False, rms_norm_weight=None, residual=None, round_dtype=None, eps=1e-5):
+    """The reference's GDPA-plus-norm pipeline, forward, in fp32:
+    ``q' = LayerNorm(query)`` over heads * head_dim (rounded to ``round_dtype`` like the reference, which keeps it
+    in the input dtype), ``x = GDPA(q', K, V) [+ q']``, ``y = x * rsqrt(mean(x^2) + eps) [* w]``, ``[+ residual]``.
+    Follows the eager formulation of gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:67-74 and :110-127 and the
+    order of the kernel epilogue (gdpa_megakernel/src/tlx_gdpa_megakernel.py:1076-1142: Q residual before the
+    norm, generic residual after it; eps 1e-5 at :402 and :481)."""
+    T, H, D = query.shape
+    q = query.to(torch.float32)
+    if fused_layernorm:
+        w = None if layernorm_weight is None else layernorm_weight.to(torch.float32).reshape(H * D)
+        b = None if layernorm_bias is None else layernorm_bias.to(torch.float32).reshape(H * D)
+        q = torch.nn.functional.layer_norm(q.reshape(T, H * D), (H * D,), w, b, eps).reshape(T, H, D)
+        if round_dtype is not None:
+            q = q.to(round_dtype).to(torch.float32)
+    x = gdpa_forward(q, key, value, query_offset, key_offset, activation, qk_scale)
+    if fused_q_residual_add:
+        x = x + q
+    if fused_rms_norm:
+        x2 = x.reshape(T, H * D)
+        x2 = x2 * torch.rsqrt(x2.pow(2).mean(dim=1, keepdim=True) + eps)
+        if rms_norm_weight is not None:
+            x2 = x2 * rms_norm_weight.to(torch.float32).reshape(1, H * D)
+        x = x2.reshape(T, H, D)
+    if residual is not None:
+        x = x + residual.to(torch.float32)
+    return x
+
+
 def gdpa_backward_formulas(
     query: torch.Tensor,
     key: torch.Tensor,

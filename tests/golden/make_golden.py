@@ -18,8 +18,9 @@ symlink of that name makes them resolve.  Four things are recorded:
   forward op body (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335) and the backward
   op body (:3461-3788), executed on the CPU by Triton's interpreter (``TRITON_INTERPRET=1``, autotuning
   off), on a jagged batch with different Q and KV lengths and ``qk_scale = 0.25``, for every activation
-  of the table; plus one grouped-query case (4 query heads, 2 K/V heads) and one banded case
-  (``window_size = 6``).  These pin where the scale is applied and every gradient;
+  of the table; plus one grouped-query case (4 query heads, 2 K/V heads), one banded case
+  (``window_size = 6``), one case with per-head activations (``ensemble_activation_list``) and one with
+  ``broadcast_q``.  These pin where the scale is applied and every gradient;
 * ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
 
 Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
@@ -144,6 +145,28 @@ def main(ref_root: str) -> None:
                activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
     out.update(window_size=np.int32(W), window_o=ow.numpy(), window_dq=resw[0].numpy(), window_dk=resw[1].numpy(),
                window_dv=resw[2].numpy())
+
+    # per-head activations: head 0 relu, head 1 leaky_relu (base activation raw)
+    ens = [ref_math.activation_to_int[ref_math.Activation.ReLU], ref_math.activation_to_int[ref_math.Activation.LeakyReLU]]
+    oe = fwd(q, k, v, qo, ko, int(lq.max()), int(lk.max()), qk_scale=scale, activation="raw", ensemble_activation_list=ens)
+    rese = bwd(do, q, k, v, oe, qo, ko, B, H, 1, int(lq.max()), int(lk.max()), D, D, qk_scale=scale,
+               activation_enum_int=0, ensemble_activation_list=ens)
+    out.update(ensemble_ids=np.array(ens, dtype=np.int32), ensemble_o=oe.numpy(), ensemble_dq=rese[0].numpy(),
+               ensemble_dk=rese[1].numpy(), ensemble_dv=rese[2].numpy())
+
+    # broadcast_q: one Q sequence of 9 rows attended with by every KV sequence; output rows of batch element z
+    # at output_offset[z]; dQ summed over the batch
+    LB = 9
+    qb = torch.randn(LB, H, D, generator=g)
+    qob = torch.tensor([0, LB], dtype=torch.int32)
+    oob = torch.arange(B + 1, dtype=torch.int32) * LB
+    dob = torch.randn(B * LB, H, D, generator=g)
+    ob = fwd(qb, k, v, qob, ko, LB, int(lk.max()), qk_scale=scale, output_offset=oob, broadcast_q=True,
+             activation="gelu_approx")
+    resb = bwd(dob, qb, k, v, ob, qob, ko, B, H, 1, LB, int(lk.max()), D, D, qk_scale=scale, output_offset=oob,
+               broadcast_q=True, activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
+    out.update(bcast_q=qb.numpy(), bcast_do=dob.numpy(), bcast_o=ob.numpy(), bcast_dq=resb[0].float().numpy(),
+               bcast_dk=resb[1].numpy(), bcast_dv=resb[2].numpy())
 
     np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
     ids = {a.value: i for a, i in ref_math.activation_to_int.items()}

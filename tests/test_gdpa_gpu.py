@@ -372,3 +372,66 @@ def test_banded_attention_window_size(G, act, window):
         o2 = G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], max(lq), max(lk),
                                                  qk_scale=0.1, activation=act)
         assert torch.equal(o2, o)
+
+
+@pytest.mark.parametrize("hq,hkv,ids", [
+    (4, 4, [5, 5, 7]),          # relu, relu, silu, then the base activation for head 3
+    (4, 2, [2, 2, 10, 10]),     # grouped-query, whole groups agree
+    (4, 2, [2, 5, 5, 5, 9]),    # grouped-query, the first group is mixed; list longer than H is cut
+])
+def test_per_head_activations_ensemble(G, hq, hkv, ids):
+    """ensemble_activation_list: head i < len(list) uses activation id list[i], the others the base."""
+    lq, lk = [130, 40, 257], [200, 129, 64]
+    g = torch.Generator().manual_seed(17)
+    qo = torch.tensor(np.concatenate([[0], np.cumsum(lq)]))
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    q = (torch.randn(int(qo[-1]), hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(int(ko[-1]), hkv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(int(ko[-1]), hkv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    do = (torch.randn(int(qo[-1]), hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = G.generalized_dot_product_attention(qd, kd, vd, qo.cuda(), ko.cuda(), max(lq), max(lk), qk_scale=1.0 / 64,
+                                            activation="gelu_approx", ensemble_activation_list=ids)
+    o.backward(do.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    from oracle import gdpa_oracle as orc
+    from ads_model_kernel_library_b200.gdpa.math import int_to_activation
+    names = [int_to_activation[ids[h]].value if h < len(ids) else "gelu_approx" for h in range(hq)]
+    ro, rdq, rdk, rdv = orc.forward_backward_of(
+        lambda a, b, c: orc.gdpa_forward_ensemble(a, b, c, qo, ko, names, 1.0 / 64), q.float(), k.float(), v.float(), do.float())
+    assert o.shape == q.shape and o.is_contiguous()
+    for a, b, n in ((o, ro, "O"), (qd.grad, rdq, "dQ"), (kd.grad, rdk, "dK"), (vd.grad, rdv, "dV")):
+        assert_close(a, b, f"{n}[ensemble {ids}]")
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(qd, kd, vd, qo.cuda(), ko.cuda(), max(lq), max(lk),
+                                            ensemble_activation_list=[42])
+
+
+@pytest.mark.parametrize("act", ["gelu_approx", "softmax"])
+def test_broadcast_q_one_query_sequence_for_the_batch(G, act):
+    """broadcast_q: query holds one sequence; output [B * Lq, H, D], dQ summed over the batch."""
+    LQ, lk, H = 150, [200, 129, 64, 1], 2
+    g = torch.Generator().manual_seed(23)
+    ko = torch.tensor(np.concatenate([[0], np.cumsum(lk)]))
+    q = (torch.randn(LQ, H, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k = (torch.randn(int(ko[-1]), H, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v = (torch.randn(int(ko[-1]), H, 128, generator=g) * 0.5).to(torch.bfloat16)
+    do = (torch.randn(len(lk) * LQ, H, 128, generator=g) * 0.5).to(torch.bfloat16)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    qo = torch.tensor([0, LQ]).cuda()
+    oo = (torch.arange(len(lk) + 1) * LQ).cuda()
+    o = G.generalized_dot_product_attention(qd, kd, vd, qo, ko.cuda(), LQ, max(lk), qk_scale=0.1, activation=act,
+                                            broadcast_q=True, output_offset=oo)
+    o.backward(do.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    from oracle import gdpa_oracle as orc
+    ro, rdq, rdk, rdv = orc.forward_backward_of(
+        lambda a, b, c: orc.gdpa_forward_broadcast_q(a, b, c, ko, act, 0.1), q.float(), k.float(), v.float(), do.float())
+    assert o.shape == (len(lk) * LQ, H, 128) and qd.grad.shape == q.shape
+    for a, b, n in ((o, ro, "O"), (qd.grad, rdq, "dQ"), (kd.grad, rdk, "dK"), (vd.grad, rdv, "dV")):
+        assert_close(a, b, f"{n}[broadcast_q {act}]")
+    o2 = G.generalized_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), qo, ko.cuda(), LQ, max(lk), qk_scale=0.1,
+                                             activation=act, broadcast_q=True)
+    assert torch.equal(o2, o)

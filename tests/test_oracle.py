@@ -111,3 +111,46 @@ def test_oracle_matches_reference_triton_kernels_banded(golden):
                                               window_size=int(golden["window_size"]))
     for name, got in (("o", o), ("dq", dq), ("dk", dk), ("dv", dv)):
         torch.testing.assert_close(got, t(f"window_{name}"), atol=2e-5, rtol=2e-5)
+
+
+def test_oracle_matches_reference_triton_kernels_per_head_activations(golden):
+    """ensemble_activation_list: head 0 relu, head 1 leaky_relu."""
+    t = lambda n: torch.from_numpy(golden[n])
+    names = {5: "relu", 4: "leaky_relu"}
+    acts = [names[int(i)] for i in golden["ensemble_ids"]]
+    scale = float(golden["triton_scale"])
+    res = orc.forward_backward_of(
+        lambda q, k, v: orc.gdpa_forward_ensemble(q, k, v, t("triton_qo"), t("triton_ko"), acts, scale),
+        t("triton_q"), t("triton_k"), t("triton_v"), t("triton_do"))
+    for name, got in zip(("o", "dq", "dk", "dv"), res):
+        torch.testing.assert_close(got, t(f"ensemble_{name}"), atol=2e-5, rtol=2e-5)
+
+
+def test_oracle_matches_reference_triton_kernels_broadcast_q(golden):
+    """broadcast_q: one Q sequence for the whole batch, output [B * Lq, H, D], dQ summed over the batch."""
+    t = lambda n: torch.from_numpy(golden[n])
+    scale = float(golden["triton_scale"])
+    res = orc.forward_backward_of(
+        lambda q, k, v: orc.gdpa_forward_broadcast_q(q, k, v, t("triton_ko"), "gelu_approx", scale),
+        t("bcast_q"), t("triton_k"), t("triton_v"), t("bcast_do"))
+    for name, got in zip(("o", "dq", "dk", "dv"), res):
+        torch.testing.assert_close(got, t(f"bcast_{name}"), atol=3e-5, rtol=3e-5)
+
+
+def test_norm_pipeline_oracle_follows_the_reference_test_formulation():
+    """LayerNorm(Q) -> GDPA -> + ln_q -> RMSNorm, written as the reference's megakernel test writes it
+    (gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:110-127) with torch's functional norms."""
+    torch.manual_seed(0)
+    T, H, D = 40, 2, 16
+    q, k, v = torch.randn(T, H, D), torch.randn(T, H, D), torch.randn(T, H, D)
+    off = torch.tensor([0, 17, 40])
+    ln_q = torch.nn.functional.layer_norm(q.view(T, -1), (H * D,), eps=1e-5).view_as(q)
+    g = orc.gdpa_forward(ln_q, k, v, off, off, "fast_gelu", None)
+    ref = torch.nn.functional.rms_norm((g + ln_q).view(T, -1), (H * D,), eps=1e-5).view_as(g)
+    out = orc.gdpa_with_norms(q, k, v, off, off, "fast_gelu", None, fused_layernorm=True, fused_q_residual_add=True,
+                              fused_rms_norm=True)
+    torch.testing.assert_close(out, ref, atol=1e-6, rtol=1e-6)
+    ref1 = torch.nn.functional.rms_norm(orc.gdpa_forward(q, k, v, off, off, "fast_gelu", None).view(T, -1), (H * D,),
+                                        eps=1e-5).view_as(g)
+    torch.testing.assert_close(orc.gdpa_with_norms(q, k, v, off, off, "fast_gelu", None, fused_rms_norm=True), ref1,
+                               atol=1e-6, rtol=1e-6)
