@@ -172,6 +172,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--e2e-chunks", type=int, default=16)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
+    ap.add_argument("--norms", action="store_true",
+                    help="time the forward of the GDPA-plus-norm pipeline (layer norm of Q, Q residual, RMS norm) "
+                         "instead of the workload's own pass, and the two row-norm kernels against the HBM roofline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-flops", type=float, default=None, help="useful FLOPs of the CPU sample per step of the reference arm")
@@ -206,8 +209,11 @@ def main():
         w.activation = args.activation
     strong = args.workload == "c5_zipf_sharded"
     fp8 = args.workload == "c4_fp8_softmax"
+    if args.norms:
+        assert not fp8 and w.activation != "softmax", "--norms needs a bf16 workload with an element-wise activation"
+        w.mode = "fwd"
     fwd_only = w.mode == "fwd"
-    metric = METRIC if not fwd_only else "gdpa_fwd_useful_tflops"
+    metric = METRIC if not fwd_only else ("gdpa_fwd_norms_useful_tflops" if args.norms else "gdpa_fwd_useful_tflops")
     if strong:
         # token-balanced contiguous ranges; a rank's range is streamed in pieces that fit in HBM
         pieces_per_rank = max(1, 8 // world)
@@ -235,7 +241,11 @@ def main():
         for b in batches:
             if fwd_only:
                 with torch.no_grad():
-                    if fp8:
+                    if args.norms:
+                        G.gdpa_megakernel(b["q"], b["k"], b["v"], b["q_offsets"], b["kv_offsets"], b["max_q"], b["max_kv"],
+                                          qk_scale=w.qk_scale, activation=w.activation, fused_layernorm=True,
+                                          fused_q_residual_add=True, fused_rms_norm=True)
+                    elif fp8:
                         G.generalized_dot_product_attention_fp8(b["q8"], b["k8"], b["v8"], b["sq"], b["sk"], b["sv"], b["qb"],
                                                                 b["kb"], b["q_offsets"], b["kv_offsets"], b["max_q"],
                                                                 b["max_kv"], qk_scale=w.qk_scale, activation=w.activation)
@@ -319,6 +329,29 @@ def main():
                     "algorithmic_bytes": 16.0 * w.heads * w.head_dim * float(last["lq"].sum()),
                     "kernel_ms": bwd_ms, "fwd_kernel": fwd_part, "frac_of_nominal_2250": achieved / 2250.0}
 
+    if args.norms:
+        # the two row-norm kernels alone against the HBM roofline: each reads and writes one bf16 [T, H, D] tensor
+        x = last["q"].detach()
+        sumsq = torch.ones(x.shape[0], dtype=torch.float32, device=dev)
+        nbytes = 2.0 * x.numel() * x.element_size()
+        hbm = peaks["hbm_gbs"]
+        norm_part = {}
+        for name, fn in (("gdpa_layernorm_rows_kernel", lambda: G.layernorm_rows(x)),
+                         ("gdpa_rmsnorm_rows_kernel", lambda: G.rmsnorm_rows(x, row_sumsq=sumsq))):
+            for _ in range(3):
+                fn()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b_) / 10
+            norm_part[name] = {"bound": "hbm", "kernel_ms": ms, "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": hbm,
+                               "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / hbm, "algorithmic_bytes": nbytes,
+                               "note": "timed with the output allocation of the Python wrapper inside the loop"}
+        roofline["norm_kernels"] = norm_part
+
     # ---- end to end: pinned host buffers, H2D of the inputs and D2H of every result per step ----
     e2e = None
     if not args.no_e2e and not strong and not fwd_only:
@@ -363,7 +396,7 @@ def main():
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": int(sum(len(b["lq"]) for b in batches)), "heads": w.heads,
-                       "head_dim": w.head_dim, "activation": w.activation, "pass": "fwd" if fwd_only else "fwd+bwd",
+                       "head_dim": w.head_dim, "activation": w.activation, "pass": ("fwd+norms" if args.norms else "fwd") if fwd_only else "fwd+bwd",
                        "tokens_per_step": int(total_tokens), "useful_tflop_per_step": total_flops / 1e12,
                        "l2": "inputs larger than L2 (each of Q, K, V, dO exceeds 126 MB), no flush",
                        "parallelism": f"batch sharded by sequence over {world} GPU(s), no collective"},
