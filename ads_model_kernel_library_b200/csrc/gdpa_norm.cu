@@ -22,7 +22,6 @@ namespace gdpa {
 namespace {
 
 constexpr int kNormThreads = 256;         // 8 rows per block
-constexpr int kCachedChunks = 8;          // 16-byte chunks a lane keeps in registers (N <= 32 * 8 * 8)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -54,7 +53,11 @@ __device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
 }
 
 // y = (x - mean) * rstd * weight + bias per row; mean and the (biased) variance over the N values of the row,
-// variance from the centred values like torch.nn.functional.layer_norm.
+// variance from the centred values like torch.nn.functional.layer_norm.  A lane keeps up to kCachedChunks
+// 16-byte chunks of the row in registers between the passes (rows of up to 256 * kCachedChunks values; the
+// instantiation is chosen by the row length, fewer registers giving more rows in flight); longer rows are
+// read again.
+template <int kCachedChunks>
 __global__ void __launch_bounds__(kNormThreads) gdpa_layernorm_rows_kernel(const NormArgs a) {
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (kNormThreads / 32) + (threadIdx.x >> 5);
@@ -180,7 +183,10 @@ __global__ void __launch_bounds__(kNormThreads) gdpa_rmsnorm_rows_kernel(const N
 int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream) {
   if (a.rows == 0) return 0;
   const long long blocks = (a.rows + kNormThreads / 32 - 1) / (kNormThreads / 32);
-  gdpa_layernorm_rows_kernel<<<static_cast<unsigned>(blocks), kNormThreads, 0, stream>>>(a);
+  const unsigned grid = static_cast<unsigned>(blocks);
+  if (a.n <= 512) gdpa_layernorm_rows_kernel<2><<<grid, kNormThreads, 0, stream>>>(a);
+  else if (a.n <= 1024) gdpa_layernorm_rows_kernel<4><<<grid, kNormThreads, 0, stream>>>(a);
+  else gdpa_layernorm_rows_kernel<8><<<grid, kNormThreads, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 
