@@ -89,7 +89,12 @@ struct BwdSmem {
 
 // How dQ tiles leave the SM: staged in shared memory and added by TMA reduce (full 128-byte lines at
 // L2, but 128 KB of shared-memory traffic per tile), or straight from registers with vector reductions.
-// Two alternatives were measured on the B=512 uniform workload and dropped.  (1) Adding dQ tiles to the
+// Three alternatives were measured on the B=512 uniform workload and dropped.  (0) Sixteen element-wise warps
+// (four column quarters) instead of eight: the phases did not get shorter (2 000 and 770 cycles per Q tile
+// against 2 180 and 740: they are bound by FMA-pipe and issue throughput of the four SM sub-partitions, not by
+// latency), and the dQ drain, left with 80 registers, released TMEM later: 5 830 instead of 4 570 cycles per
+// Q tile.  (setmaxnreg only moves registers inside the CTA's own allocation: increases that ask for more than
+// the decreases free wait forever.)  (1) Adding dQ tiles to the
 // accumulator straight from registers with red.global.add.v4.f32 (no shared-memory staging): 578 instead
 // of 803 TFLOP/s, the 16-byte reductions to 32 different 128-byte lines per instruction saturate the
 // LSU / L2 path.  (2) Reading the A operand of dK from shared memory and issuing dQ before dK (the drain

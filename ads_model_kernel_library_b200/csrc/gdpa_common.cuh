@@ -257,12 +257,13 @@ __device__ __forceinline__ void act_and_grad_pair(float x0, float x1, float scal
     unpack_f32x2(mul_f32x2(X, fma_f32x2(X2, pack_f32x2(c0 * c1, c0 * c1), pack_f32x2(c0, c0))), u0, u1);
     const uint64_t T = pack_f32x2(tanh_approx(u0), tanh_approx(u1));
     const uint64_t HS = pack_f32x2(hscale, hscale);
-    const uint64_t XS = mul_f32x2(X, HS);
-    const uint64_t P = fma_f32x2(XS, T, XS);
+    // with s = hscale (1 + t):  p = x s  and  p' = s + p (1 - t) du   (1 - t^2 = (1 - t)(1 + t)); nine packed
+    // operations per pair instead of thirteen, and the element-wise phase is bound by the FMA pipe
+    const uint64_t S = fma_f32x2(T, HS, HS);
+    const uint64_t P = mul_f32x2(X, S);
     const uint64_t DU = fma_f32x2(X2, pack_f32x2(3.f * c0 * c1, 3.f * c0 * c1), pack_f32x2(c0, c0));
-    const uint64_t NT = mul_f32x2(T, pack_f32x2(-1.f, -1.f));
-    const uint64_t SECH2 = fma_f32x2(NT, T, pack_f32x2(1.f, 1.f));
-    const uint64_t G = fma_f32x2(mul_f32x2(XS, SECH2), DU, fma_f32x2(T, HS, HS));
+    const uint64_t OMT = fma_f32x2(T, pack_f32x2(-1.f, -1.f), pack_f32x2(1.f, 1.f));
+    const uint64_t G = fma_f32x2(mul_f32x2(P, DU), OMT, S);
     unpack_f32x2(P, p0, p1);
     if constexpr (!MASKED) {
       p_bf16x2 = pack_bf16x2(p0, p1);
@@ -275,10 +276,10 @@ __device__ __forceinline__ void act_and_grad_pair(float x0, float x1, float scal
     float h0, h1;
     unpack_f32x2(mul_f32x2(X, pack_f32x2(0.5f, 0.5f)), h0, h1);
     const uint64_t T = pack_f32x2(tanh_approx(h0), tanh_approx(h1));
-    const uint64_t SG = fma_f32x2(T, pack_f32x2(0.5f, 0.5f), pack_f32x2(0.5f, 0.5f));
-    const uint64_t SGS = mul_f32x2(SG, pack_f32x2(scale, scale));
+    // sg * scale and 1 - sg, each one fma of t
+    const uint64_t SGS = fma_f32x2(T, pack_f32x2(hscale, hscale), pack_f32x2(hscale, hscale));
     const uint64_t P = mul_f32x2(X, SGS);
-    const uint64_t OM = fma_f32x2(SG, pack_f32x2(-1.f, -1.f), pack_f32x2(1.f, 1.f));
+    const uint64_t OM = fma_f32x2(T, pack_f32x2(-0.5f, -0.5f), pack_f32x2(0.5f, 0.5f));
     const uint64_t G = mul_f32x2(SGS, fma_f32x2(X, OM, pack_f32x2(1.f, 1.f)));
     unpack_f32x2(P, p0, p1);
     if constexpr (!MASKED) {
