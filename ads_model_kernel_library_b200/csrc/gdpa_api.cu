@@ -311,6 +311,35 @@ int gdpa_rmsnorm_rows(const GdpaNormParams* p, gdpa_stream_t stream) {
   return rc;
 }
 
+int gdpa_norm_rows_bwd(const GdpaNormBwdParams* p, gdpa_stream_t stream) {
+  if (p == nullptr || p->struct_size != sizeof(GdpaNormBwdParams)) return GDPA_ERR_BAD_ARG;
+  if (p->mode < 0 || p->mode > 2 || p->rows < 0 || p->n <= 0 || p->n % 8 != 0) return GDPA_ERR_BAD_ARG;
+  if (p->rows > 0 && (p->dy == nullptr || p->dx == nullptr)) return GDPA_ERR_BAD_ARG;
+  if (p->rows > 0 && p->mode != 2 && (p->x == nullptr || p->row_rstd == nullptr)) return GDPA_ERR_BAD_ARG;
+  if (p->rows > 0 && p->mode == 1 && p->row_mean == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->mode == 2 && p->dy_add == nullptr) return GDPA_ERR_BAD_ARG;
+  if ((p->dweight != nullptr || p->dbias != nullptr) && p->n > 4096) return GDPA_ERR_BAD_ARG;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(p->dy) | reinterpret_cast<uintptr_t>(p->dy_add) |
+                          reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->dx) |
+                          reinterpret_cast<uintptr_t>(p->weight);
+  if ((align & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  NormBwdArgs a;
+  a.dy = static_cast<const __nv_bfloat16*>(p->dy);
+  a.dy_add = static_cast<const __nv_bfloat16*>(p->dy_add);
+  a.x = static_cast<const __nv_bfloat16*>(p->x);
+  a.dx = static_cast<__nv_bfloat16*>(p->dx);
+  a.weight = p->mode == 2 ? nullptr : p->weight;
+  a.row_mean = p->row_mean;
+  a.row_rstd = p->row_rstd;
+  a.dweight = p->dweight;
+  a.dbias = p->dbias;
+  a.rows = p->rows;
+  a.n = p->n;
+  const int rc = launch_norm_rows_bwd(a, p->mode, static_cast<cudaStream_t>(stream));
+  if (rc == 0 && a.rows > 0) g_launches.fetch_add(1);
+  return rc;
+}
+
 int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   int rc = check_common(p);
   if (rc != GDPA_OK) return rc;

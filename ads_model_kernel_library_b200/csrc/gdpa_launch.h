@@ -58,6 +58,20 @@ struct NormArgs {
   float eps;
 };
 
+struct NormBwdArgs {
+  const __nv_bfloat16* dy;
+  const __nv_bfloat16* dy_add;
+  const __nv_bfloat16* x;
+  __nv_bfloat16* dx;
+  const float* weight;
+  const float* row_mean;
+  const float* row_rstd;
+  float* dweight;
+  float* dbias;
+  long long rows;
+  int n;
+};
+
 struct FwdLaunch {
   CUtensorMap tm_q, tm_k, tm_v;
   FwdArgs args;
@@ -117,6 +131,7 @@ int launch_dpsum(const __nv_bfloat16* d_o, const __nv_bfloat16* o, float* dpsum,
 int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream);
 int launch_rmsnorm_rows(const NormArgs& a, cudaStream_t stream);
+int launch_norm_rows_bwd(const NormBwdArgs& a, int mode, cudaStream_t stream);
 int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
 
 }  // namespace gdpa

@@ -9,7 +9,8 @@
 // head (gdpa_megakernel/src/tlx_gdpa_megakernel.py:359-405 RMS norm, :412-500 layer norm, :1076-1135
 // epilogue order; checked by gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:50-145).  Both kernels are
 // HBM-bound streaming passes: one warp per token row of N = heads * head_dim bf16 values, 16-byte loads,
-// fp32 statistics, the row kept in registers between the statistics and the write when N <= 2048.
+// fp32 statistics, the row kept in registers between the statistics and the write when N <= 2048.  The backward
+// of both norms (gdpa_norm_rows_bwd_kernel) follows the same row-per-warp scheme on a persistent grid.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -178,6 +179,113 @@ __global__ void __launch_bounds__(kNormThreads) gdpa_rmsnorm_rows_kernel(const N
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Backward of the two row norms.  One warp per row, persistent grid; lanes own fixed columns, so the weight / bias
+// gradients (sums over rows) are collected per block in shared memory and flushed with one global atomic per
+// column and block.
+constexpr int kNormBwdMaxN = 4096;  // weight / bias gradients are supported up to this row length
+
+// RMS norm  y = x r w,  r = rsqrt(mean(x^2) + eps)  (r saved by the forward):
+//   g = dy w;  dx = r g - x r^3 mean(g x);  dw += dy x r.
+// Layer norm  y = xh rstd' ...  with xh = (x - mean) rstd (mean, rstd saved by the forward):
+//   g = (dy + dy_add) w;  dx = rstd (g - mean(g) - xh mean(g xh));  dw += (dy + dy_add) xh;  db += dy + dy_add.
+// `dy_add` is an optional second incoming gradient of the same shape (the Q-residual branch of the pipeline).
+// With mode 2 there is no norm: dx = dy + dy_add.
+template <int MODE>  // 0 = RMS norm, 1 = layer norm, 2 = plain sum
+__global__ void __launch_bounds__(kNormThreads) gdpa_norm_rows_bwd_kernel(const NormBwdArgs a) {
+  __shared__ float s_dw[MODE == 2 ? 1 : kNormBwdMaxN];
+  __shared__ float s_db[MODE == 1 ? kNormBwdMaxN : 1];
+  const int lane = threadIdx.x & 31;
+  const int chunks = a.n / 8;
+  const bool want_dw = MODE != 2 && a.dweight != nullptr;
+  const bool want_db = MODE == 1 && a.dbias != nullptr;
+  if (want_dw || want_db) {
+    for (int i = threadIdx.x; i < a.n; i += kNormThreads) {
+      if (want_dw) s_dw[i] = 0.f;
+      if (want_db) s_db[i] = 0.f;
+    }
+    __syncthreads();
+  }
+  const long long warps = static_cast<long long>(gridDim.x) * (kNormThreads / 32);
+  const float inv_n = 1.f / static_cast<float>(a.n);
+  for (long long row = static_cast<long long>(blockIdx.x) * (kNormThreads / 32) + (threadIdx.x >> 5); row < a.rows; row += warps) {
+    const uint4* dy = reinterpret_cast<const uint4*>(a.dy + row * a.n);
+    const uint4* dy2 = a.dy_add != nullptr ? reinterpret_cast<const uint4*>(a.dy_add + row * a.n) : nullptr;
+    const uint4* x = MODE != 2 ? reinterpret_cast<const uint4*>(a.x + row * a.n) : nullptr;
+    uint4* dx = reinterpret_cast<uint4*>(a.dx + row * a.n);
+    const float rstd = MODE != 2 ? a.row_rstd[row] : 1.f;
+    const float mean = MODE == 1 ? a.row_mean[row] : 0.f;
+    // pass 1: the row sums
+    float s1 = 0.f, s2 = 0.f;
+    if (MODE != 2) {
+      for (int c = lane; c < chunks; c += 32) {
+        float g[8], xv[8], w[8];
+        unpack8(dy[c], g);
+        if (dy2 != nullptr) {
+          float t[8];
+          unpack8(dy2[c], t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] += t[j];
+        }
+        unpack8(x[c], xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = 1.f;
+        if (a.weight != nullptr) load8(a.weight + 8 * c, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gw = g[j] * w[j];
+          const float xh = MODE == 1 ? (xv[j] - mean) * rstd : xv[j];
+          s1 += gw;
+          s2 = fmaf(gw, xh, s2);
+        }
+      }
+      s1 = warp_sum(s1) * inv_n;
+      s2 = warp_sum(s2) * inv_n;
+    }
+    // pass 2: dx and the column sums (the row is read again; it sits in L1 / L2)
+    for (int c = lane; c < chunks; c += 32) {
+      float g[8], xv[8], w[8], o[8];
+      unpack8(dy[c], g);
+      if (dy2 != nullptr) {
+        float t[8];
+        unpack8(dy2[c], t);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += t[j];
+      }
+      if (MODE == 2) {
+        dx[c] = pack8(g);
+        continue;
+      }
+      unpack8(x[c], xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = 1.f;
+      if (a.weight != nullptr) load8(a.weight + 8 * c, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gw = g[j] * w[j];
+        if (MODE == 0) {
+          // dx = r g - x r^3 mean(g x)
+          o[j] = rstd * (gw - xv[j] * rstd * rstd * s2);
+          if (want_dw) atomicAdd(&s_dw[8 * c + j], g[j] * xv[j] * rstd);
+        } else {
+          const float xh = (xv[j] - mean) * rstd;
+          o[j] = rstd * (gw - s1 - xh * s2);
+          if (want_dw) atomicAdd(&s_dw[8 * c + j], g[j] * xh);
+          if (want_db) atomicAdd(&s_db[8 * c + j], g[j]);
+        }
+      }
+      dx[c] = pack8(o);
+    }
+  }
+  if (want_dw || want_db) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.n; i += kNormThreads) {
+      if (want_dw) atomicAdd(a.dweight + i, s_dw[i]);
+      if (want_db) atomicAdd(a.dbias + i, s_db[i]);
+    }
+  }
+}
+
 }  // namespace
 
 int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream) {
@@ -194,6 +302,18 @@ int launch_rmsnorm_rows(const NormArgs& a, cudaStream_t stream) {
   if (a.rows == 0) return 0;
   const long long blocks = (a.rows + kNormThreads / 32 - 1) / (kNormThreads / 32);
   gdpa_rmsnorm_rows_kernel<<<static_cast<unsigned>(blocks), kNormThreads, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
+}
+
+// mode: 0 = RMS norm, 1 = layer norm, 2 = plain sum of the two incoming gradients
+int launch_norm_rows_bwd(const NormBwdArgs& a, int mode, cudaStream_t stream) {
+  if (a.rows == 0) return 0;
+  long long blocks = (a.rows + kNormThreads / 32 - 1) / (kNormThreads / 32);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const unsigned grid = static_cast<unsigned>(blocks);
+  if (mode == 0) gdpa_norm_rows_bwd_kernel<0><<<grid, kNormThreads, 0, stream>>>(a);
+  else if (mode == 1) gdpa_norm_rows_bwd_kernel<1><<<grid, kNormThreads, 0, stream>>>(a);
+  else gdpa_norm_rows_bwd_kernel<2><<<grid, kNormThreads, 0, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 

@@ -27,6 +27,7 @@ EXPORTS = (
     "gdpa_fwd_noalloc",
     "gdpa_layernorm_rows",
     "gdpa_rmsnorm_rows",
+    "gdpa_norm_rows_bwd",
     "gdpa_bwd_workspace_bytes",
     "gdpa_bwd",
     "gdpa_strerror",
@@ -114,6 +115,25 @@ class GdpaNormParams(C.Structure):
     ]
 
 
+class GdpaNormBwdParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("mode", C.c_int32),
+        ("rows", C.c_int64),
+        ("n", C.c_int32),
+        ("reserved", C.c_int32),
+        ("dy", C.c_void_p),
+        ("dy_add", C.c_void_p),
+        ("x", C.c_void_p),
+        ("dx", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("row_mean", C.c_void_p),
+        ("row_rstd", C.c_void_p),
+        ("dweight", C.c_void_p),
+        ("dbias", C.c_void_p),
+    ]
+
+
 class GdpaBwdParams(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32),
@@ -171,6 +191,8 @@ def _load() -> C.CDLL:
     for fn in (lib.gdpa_layernorm_rows, lib.gdpa_rmsnorm_rows):
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(GdpaNormParams), C.c_void_p]
+    lib.gdpa_norm_rows_bwd.restype = C.c_int
+    lib.gdpa_norm_rows_bwd.argtypes = [C.POINTER(GdpaNormBwdParams), C.c_void_p]
     lib.gdpa_fwd_fp8.restype = C.c_int
     lib.gdpa_fwd_fp8.argtypes = [C.POINTER(GdpaFwdParams), C.c_void_p]
     lib.gdpa_bwd_workspace_bytes.restype = C.c_size_t

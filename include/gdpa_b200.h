@@ -229,6 +229,32 @@ int gdpa_layernorm_rows(const GdpaNormParams* params, gdpa_stream_t stream);
 /* out = x / sqrt(mean(x^2) + eps) * weight + residual per row. */
 int gdpa_rmsnorm_rows(const GdpaNormParams* params, gdpa_stream_t stream);
 
+/* Backward of the two row norms (and the plain sum of two incoming gradients), for training through the
+ * GDPA-plus-norm pipeline.  `mode`: 0 = RMS norm, 1 = layer norm, 2 = dx = dy + dy_add.
+ *   RMS norm:   g = dy w;             dx = r (g - x r^2 mean(g x));            dweight += dy x r
+ *   layer norm: g = (dy + dy_add) w;  dx = rstd (g - mean(g) - xh mean(g xh));  dweight += (dy + dy_add) xh;
+ *               dbias += dy + dy_add,  xh = (x - mean) rstd
+ * with r / mean / rstd the per-row statistics the forward entry points write (row_rstd, row_mean).  dweight and
+ * dbias ([n] fp32, optional, n <= 4096) are added to: the caller zeroes them. */
+typedef struct GdpaNormBwdParams {
+  uint32_t struct_size;   /* sizeof(GdpaNormBwdParams) */
+  int32_t mode;
+  int64_t rows;
+  int32_t n;
+  int32_t reserved;
+  const void* dy;         /* [rows, n] bf16 */
+  const void* dy_add;     /* optional [rows, n] bf16, added to dy */
+  const void* x;          /* [rows, n] bf16: the input of the norm (modes 0, 1) */
+  void* dx;               /* [rows, n] bf16 */
+  const float* weight;    /* optional [n] fp32 */
+  const float* row_mean;  /* [rows] fp32 (mode 1) */
+  const float* row_rstd;  /* [rows] fp32 (modes 0, 1) */
+  float* dweight;         /* optional [n] fp32 */
+  float* dbias;           /* optional [n] fp32 (mode 1) */
+} GdpaNormBwdParams;
+
+int gdpa_norm_rows_bwd(const GdpaNormBwdParams* params, gdpa_stream_t stream);
+
 /* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule
  * gdpa/src/interface.py:1053). */

@@ -104,3 +104,49 @@ def test_norm_pipeline_argument_errors(G):
         G.gdpa_megakernel(*args, is_causal=True)
     with pytest.raises(NotImplementedError):
         G.gdpa_megakernel(*args, activation="softmax", fused_rms_norm=True)
+
+
+@pytest.mark.parametrize("case", ["rms", "ln_qres_rms", "all_weights", "qres_only", "residual_only"])
+def test_norm_pipeline_backward_against_autograd_of_the_oracle(G, case):
+    """Gradients of every input of the pipeline (Q, K, V, the norm weights / bias, the residual) against
+    torch.autograd over the fp32 oracle."""
+    lq, lk, heads, D = [300, 1, 129, 257], [260, 70, 131, 50], 2, 128
+    cpu, dev = jagged_inputs(lq, lk, heads, D, seed=12, std=0.7)
+    g = torch.Generator().manual_seed(13)
+    n, T = heads * D, sum(lq)
+    kw = {
+        "rms": dict(fused_rms_norm=True),
+        "ln_qres_rms": dict(fused_layernorm=True, fused_q_residual_add=True, fused_rms_norm=True),
+        "all_weights": dict(fused_layernorm=True, layernorm_weight=1 + 0.1 * torch.randn(n, generator=g),
+                            layernorm_bias=0.1 * torch.randn(n, generator=g), fused_q_residual_add=True, fused_rms_norm=True,
+                            rms_norm_weight=1 + 0.1 * torch.randn(n, generator=g), fused_residual_add=True,
+                            residual=torch.randn(T, heads, D, generator=g).to(torch.bfloat16)),
+        "qres_only": dict(fused_q_residual_add=True),
+        "residual_only": dict(fused_residual_add=True, residual=torch.randn(T, heads, D, generator=g).to(torch.bfloat16)),
+    }[case]
+    dout = (torch.randn(T, heads, D, generator=g) * 0.5).to(torch.bfloat16)
+    scale, act = 1.0 / 64, "gelu_approx"
+    # ---- GPU
+    names = [k for k, v in kw.items() if isinstance(v, torch.Tensor)]
+    dkw = {k: (v.cuda().requires_grad_(True) if isinstance(v, torch.Tensor) else v) for k, v in kw.items()}
+    q, k, v = (dev[x].clone().requires_grad_(True) for x in ("q", "k", "v"))
+    out = G.gdpa_megakernel(q, k, v, dev["qo"], dev["ko"], max(lq), max(lk), qk_scale=scale, activation=act, **dkw)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    # ---- oracle with autograd
+    okw = {k: (v.float().clone().requires_grad_(True) if isinstance(v, torch.Tensor) else v) for k, v in kw.items()}
+    okw.pop("fused_residual_add", None)
+    rq, rk, rv = (cpu[x].float().clone().requires_grad_(True) for x in ("q", "k", "v"))
+    ref = orc.gdpa_with_norms(rq, rk, rv, cpu["qo"], cpu["ko"], act, scale, round_dtype=torch.bfloat16, **okw)
+    ref.backward(dout.float())
+    assert_close(out, ref, f"out[{case}]", atol=NORM_ATOL, rtol=NORM_RTOL)
+    for name, got, want in (("dQ", q.grad, rq.grad), ("dK", k.grad, rk.grad), ("dV", v.grad, rv.grad)):
+        assert_close(got, want, f"{name}[{case}]", atol=NORM_ATOL, rtol=NORM_RTOL)
+    for name in names:
+        want = okw[name].grad
+        got = dkw[name].grad
+        assert got is not None and got.shape == want.shape, name
+        # weight / bias gradients are sums over all tokens: compare relative to their scale
+        tol = NORM_ATOL * max(1.0, float(want.abs().max()))
+        assert_close(got, want, f"d {name}[{case}]", atol=tol, rtol=NORM_RTOL)
