@@ -399,16 +399,28 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (c == 0) tmem_ld32(tS + half * 64 + 32, rb);
           if constexpr (kSoftmax) {
             // P^T = 2^(c S^T - lse[q]) (already normalised); kept in g2 for dS = scale P (dP - dPsum)
+            // the column test in three instantiations: none on full tiles, the warp-uniform bound on edge tiles
+            // without a band, the per-thread range with a band
+            auto emit = [&](auto inside) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = half * 64 + c * 32 + 2 * i;
-              const float2 l2 = *reinterpret_cast<const float2*>(stat_lse + col);
-              float p0 = ex2_approx(fmaf(__uint_as_float(cur[2 * i]), c2, -l2.x));
-              float p1 = ex2_approx(fmaf(__uint_as_float(cur[2 * i + 1]), c2, -l2.y));
-              p0 = (col >= clo && col < chi) ? p0 : 0.f;
-              p1 = (col + 1 >= clo && col + 1 < chi) ? p1 : 0.f;
-              pk[i] = pack_bf16x2(p0, p1);
-              g2[c * 16 + i] = pack_f32x2(p0, p1);
+              for (int i = 0; i < 16; ++i) {
+                const int col = half * 64 + c * 32 + 2 * i;
+                const float2 l2 = *reinterpret_cast<const float2*>(stat_lse + col);
+                float p0 = ex2_approx(fmaf(__uint_as_float(cur[2 * i]), c2, -l2.x));
+                float p1 = ex2_approx(fmaf(__uint_as_float(cur[2 * i + 1]), c2, -l2.y));
+                p0 = inside(col) ? p0 : 0.f;
+                p1 = inside(col + 1) ? p1 : 0.f;
+                pk[i] = pack_bf16x2(p0, p1);
+                g2[c * 16 + i] = pack_f32x2(p0, p1);
+              }
+            };
+            if (full) {
+              emit([](int) { return true; });
+            } else if (a.window < 0) {
+              const int qv = min(kTile, w.lq - mm * kTile);
+              emit([&](int col) { return row_valid && col < qv; });
+            } else {
+              emit([&](int col) { return col >= clo && col < chi; });
             }
           } else if (full) {
 #pragma unroll

@@ -19,7 +19,7 @@
 //
 // Variants of the same kernel: softmax with online rescaling (the two column halves exchange their row
 // maxima through shared memory, keep partial row sums and write the log-sum-exp for the backward), and
-// FP8 e4m3 operands with per-128-token-block scales (softmax only).
+// FP8 e4m3 operands with per-128-token-block scales.
 //
 // Rows of a tile that lie beyond the end of a sequence hold other sequences' tokens (or zeros
 // past the end of the tensor): S columns beyond the KV length are set to zero before the
@@ -390,10 +390,23 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_wait_ld();
             tmem_regs_ready(cur);
             if (ch == 0) tmem_ld32(s_tmem + 32, rb);
+            // a chunk wholly inside [clo, chi) for every row of the warp needs no predicates; without a band
+            // the lower bound is 0
+            if (__all_sync(0xffffffffu, clo <= ch * 32 && chi >= (ch + 1) * 32)) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float t = __uint_as_float(cur[i]) * c;
-              pmax = (ch * 32 + i >= clo && ch * 32 + i < chi) ? fmaxf(pmax, t) : pmax;
+              for (int i = 0; i < 32; ++i) pmax = fmaxf(pmax, __uint_as_float(cur[i]) * c);
+            } else if (a.window < 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float t = __uint_as_float(cur[i]) * c;
+                pmax = (ch * 32 + i < chi) ? fmaxf(pmax, t) : pmax;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float t = __uint_as_float(cur[i]) * c;
+                pmax = (ch * 32 + i >= clo && ch * 32 + i < chi) ? fmaxf(pmax, t) : pmax;
+              }
             }
           }
           float* slot = rowmax + (((s_phase * 2 + s) * 2) * kTile);
@@ -432,29 +445,36 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_wait_ld();
             tmem_regs_ready(cur);
             if (ch == 0) tmem_ld32(s_tmem + 32, rb);
-            auto prob = [&](int i) {
-              const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
-              const float p = (ch * 32 + i >= clo && ch * 32 + i < chi) ? e : 0.f;
-              psum += p;
-              return p;
+            // P of this chunk with the column test `inside`; three instantiations so that the common case (the
+            // chunk wholly inside [clo, chi) for every row of the warp) carries no predicates at all
+            auto emit = [&](auto inside) {
+              auto prob = [&](int i) {
+                const float e = ex2_approx(fmaf(__uint_as_float(cur[i]), c, off));
+                const float p = inside(i) ? e : 0.f;
+                psum += p;
+                return p;
+              };
+              if constexpr (FP8) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float p0 = prob(4 * i), p1 = prob(4 * i + 1), p2 = prob(4 * i + 2), p3 = prob(4 * i + 3);
+                  pk[i] = pack_e4m3x4(p0 * kPScale, p1 * kPScale, p2 * kPScale, p3 * kPScale);
+                }
+                tmem_st8(s_tmem + ch * 8, pk);
+              } else {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const float p0 = prob(2 * i), p1 = prob(2 * i + 1);
+                  pk[i] = pack_bf16x2(p0, p1);
+                }
+                tmem_st16(s_tmem + ch * 16, pk);
+              }
             };
-            if constexpr (FP8) {
-              uint32_t pk[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float p0 = prob(4 * i), p1 = prob(4 * i + 1), p2 = prob(4 * i + 2), p3 = prob(4 * i + 3);
-                pk[i] = pack_e4m3x4(p0 * kPScale, p1 * kPScale, p2 * kPScale, p3 * kPScale);
-              }
-              tmem_st8(s_tmem + ch * 8, pk);
-            } else {
-              uint32_t pk[16];
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float p0 = prob(2 * i), p1 = prob(2 * i + 1);
-                pk[i] = pack_bf16x2(p0, p1);
-              }
-              tmem_st16(s_tmem + ch * 16, pk);
-            }
+            if (__all_sync(0xffffffffu, clo <= ch * 32 && chi >= (ch + 1) * 32)) emit([](int) { return true; });
+            else if (a.window < 0) emit([&](int i) { return ch * 32 + i < chi; });  // without a band the lower bound is 0
+            else emit([&](int i) { return ch * 32 + i >= clo && ch * 32 + i < chi; });
           }
           row_sum = fmaf(psum, inv_sv, row_sum);
           tmem_wait_st();
@@ -474,6 +494,20 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             a.lse[static_cast<long long>(w.h) * a.total_q + w.q_start + qr] = l_total > 0.f ? m_used + log2f(l_total) : INFINITY;
         }
       }
+      // FP8 with an element-wise activation: S = sq sk (Q8 K8^T) per tile, and P is stored as
+      // e4m3(act(S) sv_j / sv_max) with sv_max the largest V-block scale the item visits, so that every KV tile
+      // adds into the same accumulator; O = qk_scale sv_max sum_j P_j V8_j (the factor goes into the epilogue).
+      float fp8_sq = 1.f, fp8_inv_svmax = 1.f;
+      long long fp8_kv_blk0 = 0;
+      if constexpr (FP8 && !kSoftmax) {
+        const int hkv = w.h / a.kv_group;
+        fp8_sq = a.q_scales[(load_offset(a.q_blk_off, w.b, a.off64) + w.blk * 2 + s) * a.heads + w.h];
+        fp8_kv_blk0 = load_offset(a.kv_blk_off, a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, w.b, a.off64)) : w.b, a.off64);
+        float sv_max = 0.f;
+        for (int j = 0; j < nkv; ++j) sv_max = fmaxf(sv_max, a.v_scales[(fp8_kv_blk0 + j0 + j) * a.kv_heads + hkv]);
+        fp8_inv_svmax = sv_max > 0.f ? 1.f / sv_max : 0.f;
+        inv_l = a.scale * sv_max;
+      }
       for (int j = 0; !kSoftmax && j < nkv; ++j) {
         // columns [clo, chi) of this warp's 64 take part: inside the KV length and inside the band
         const int kbase = (j0 + j) * kTile + half * 64;
@@ -481,6 +515,12 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (a.window >= 0) {
           clo = max(clo, qr - a.window - kbase);
           chi = min(chi, qr + a.window - kbase + 1);
+        }
+        float fp8_xs = 1.f, fp8_g = 1.f;
+        if constexpr (FP8 && !kSoftmax) {
+          const int hkv = w.h / a.kv_group;
+          fp8_xs = fp8_sq * a.k_scales[(fp8_kv_blk0 + j0 + j) * a.kv_heads + hkv];
+          fp8_g = a.v_scales[(fp8_kv_blk0 + j0 + j) * a.kv_heads + hkv] * fp8_inv_svmax;
         }
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 0);
         GDPA_WAIT_WARP(B_S_FULL + s, s_phase, ST_ROLE_ACT);
@@ -496,6 +536,23 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_wait_ld();
           tmem_regs_ready(cur);
           if (c == 0) tmem_ld32(s_tmem + 32, rb);
+          if constexpr (FP8) {
+            // 32 values -> 32 e4m3 in 8 registers, over the first columns of this half
+            uint32_t p8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float pv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int c0 = c * 32 + 4 * i + e;
+                const float x = (c0 >= clo && c0 < chi) ? __uint_as_float(cur[4 * i + e]) * fp8_xs : 0.f;
+                pv[e] = act_scaled<ACT>(x, fp8_g, 0.5f * fp8_g);
+              }
+              p8[i] = pack_e4m3x4(pv[0], pv[1], pv[2], pv[3]);
+            }
+            tmem_st8(s_tmem + c * 8, p8);
+            continue;
+          }
           // the unmasked path is taken by the warp as a whole
           if (__all_sync(0xffffffffu, clo <= c * 32 && chi >= (c + 1) * 32)) {
 #pragma unroll
@@ -622,11 +679,21 @@ int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class) {
 
 int launch_fwd_softmax_bf16(const FwdLaunch& l, int head_dim) { return launch_fwd_bf16(l, head_dim, ACT_SOFTMAX); }
 
-// FP8 e4m3 operands: softmax only, head_dim 128 only (a 64-byte row would need the 64-byte swizzle).
+// FP8 e4m3 operands: head_dim 128 only (a 64-byte row would need the 64-byte swizzle).
 int launch_fwd_fp8(const FwdLaunch& l, int head_dim, int act_class) {
-  if (act_class != ACT_SOFTMAX) return GDPA_ERR_UNSUPPORTED_ACT_;
   if (head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM_;
-  return launch_fwd_inst<128, ACT_SOFTMAX, true>(l);
+  switch (act_class) {
+    case ACT_RAW: return launch_fwd_inst<128, ACT_RAW, true>(l);
+    case ACT_GELU_ERF: return launch_fwd_inst<128, ACT_GELU_ERF, true>(l);
+    case ACT_GELU_TANH: return launch_fwd_inst<128, ACT_GELU_TANH, true>(l);
+    case ACT_LEAKY_RELU: return launch_fwd_inst<128, ACT_LEAKY_RELU, true>(l);
+    case ACT_RELU: return launch_fwd_inst<128, ACT_RELU, true>(l);
+    case ACT_SILU: return launch_fwd_inst<128, ACT_SILU, true>(l);
+    case ACT_HARDSWISH: return launch_fwd_inst<128, ACT_HARDSWISH, true>(l);
+    case ACT_RELU_SQUARE: return launch_fwd_inst<128, ACT_RELU_SQUARE, true>(l);
+    case ACT_SOFTMAX: return launch_fwd_inst<128, ACT_SOFTMAX, true>(l);
+    default: return GDPA_ERR_UNSUPPORTED_ACT_;
+  }
 }
 
 }  // namespace gdpa

@@ -255,7 +255,8 @@ typedef struct GdpaNormBwdParams {
 
 int gdpa_norm_rows_bwd(const GdpaNormBwdParams* params, gdpa_stream_t stream);
 
-/* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16.
+/* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16; every
+ * activation, head_dim 128.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule
  * gdpa/src/interface.py:1053). */
 int gdpa_fwd_fp8(const GdpaFwdParams* params, gdpa_stream_t stream);
