@@ -46,6 +46,10 @@ constexpr int kBwdLoadWarp = 13;
 constexpr int kRegsCompute = 144;
 constexpr int kRegsReduce = 144;
 constexpr int kRegsOther = 80;
+// setmaxnreg only moves registers inside the CTA's own allocation (512 threads x 128 registers): what the
+// increases ask for must not exceed what the decreases free, or the increase never returns.
+static_assert(8 * 32 * kRegsCompute + 4 * 32 * kRegsReduce + 4 * 32 * kRegsOther <= kBwdThreads * 128,
+              "setmaxnreg budget exceeds the CTA's register allocation");
 constexpr int kDqWarpSlabBytes = 32 * 32 * 4;  // one warp's staging slab: 32 rows x 32 fp32
 
 enum BwdBar : int {
