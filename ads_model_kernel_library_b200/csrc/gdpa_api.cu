@@ -311,6 +311,30 @@ int gdpa_rmsnorm_rows(const GdpaNormParams* p, gdpa_stream_t stream) {
   return rc;
 }
 
+int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* p, gdpa_stream_t stream) {
+  if (p == nullptr || p->struct_size != sizeof(GdpaQuantParams)) return GDPA_ERR_BAD_ARG;
+  if (p->batch < 0 || p->total < 0 || p->heads <= 0 || p->head_dim <= 0 || p->head_dim % 4 != 0) return GDPA_ERR_BAD_ARG;
+  if (p->offsets == nullptr || p->block_offsets == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->total > 0 && (p->x == nullptr || p->x8 == nullptr || p->scales == nullptr)) return GDPA_ERR_BAD_ARG;
+  if (p->scale_rows < p->total / kTile + p->batch) return GDPA_ERR_CAPACITY;
+  if (p->heads > 65535) return GDPA_ERR_BAD_ARG;
+  if (((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x)) & 3u) != 0) return GDPA_ERR_MISALIGNED;
+  QuantArgs a;
+  a.x = p->x;
+  a.x8 = p->x8;
+  a.scales = p->scales;
+  a.offsets = p->offsets;
+  a.block_offsets = p->block_offsets;
+  a.off64 = p->offsets_are_int64;
+  a.batch = p->batch;
+  a.heads = p->heads;
+  a.head_dim = p->head_dim;
+  a.max_blocks = p->total > 0 ? p->total / kTile + p->batch : 0;
+  const int rc = launch_quant_fp8(a, p->in_is_fp32, static_cast<cudaStream_t>(stream));
+  if (rc == 0) g_launches.fetch_add(a.max_blocks > 0 ? 2 : 1);
+  return rc;
+}
+
 int gdpa_norm_rows_bwd(const GdpaNormBwdParams* p, gdpa_stream_t stream) {
   if (p == nullptr || p->struct_size != sizeof(GdpaNormBwdParams)) return GDPA_ERR_BAD_ARG;
   if (p->mode < 0 || p->mode > 2 || p->rows < 0 || p->n <= 0 || p->n % 8 != 0) return GDPA_ERR_BAD_ARG;

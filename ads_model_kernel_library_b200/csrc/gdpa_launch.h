@@ -58,6 +58,19 @@ struct NormArgs {
   float eps;
 };
 
+struct QuantArgs {
+  const void* x;
+  void* x8;
+  float* scales;
+  const void* offsets;
+  void* block_offsets;
+  int off64;
+  int batch;
+  int heads;
+  int head_dim;
+  long long max_blocks;  // rows of `scales`: at least total / 128 + batch
+};
+
 struct NormBwdArgs {
   const __nv_bfloat16* dy;
   const __nv_bfloat16* dy_add;
@@ -131,6 +144,7 @@ int launch_dpsum(const __nv_bfloat16* d_o, const __nv_bfloat16* o, float* dpsum,
 int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream);
 int launch_rmsnorm_rows(const NormArgs& a, cudaStream_t stream);
+int launch_quant_fp8(const QuantArgs& a, int in_is_fp32, cudaStream_t stream);
 int launch_norm_rows_bwd(const NormBwdArgs& a, int mode, cudaStream_t stream);
 int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
 

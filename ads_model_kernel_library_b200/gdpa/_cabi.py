@@ -28,6 +28,7 @@ EXPORTS = (
     "gdpa_layernorm_rows",
     "gdpa_rmsnorm_rows",
     "gdpa_norm_rows_bwd",
+    "gdpa_quantize_fp8_blockwise",
     "gdpa_bwd_workspace_bytes",
     "gdpa_bwd",
     "gdpa_strerror",
@@ -115,6 +116,24 @@ class GdpaNormParams(C.Structure):
     ]
 
 
+class GdpaQuantParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("in_is_fp32", C.c_int32),
+        ("x", C.c_void_p),
+        ("x8", C.c_void_p),
+        ("scales", C.c_void_p),
+        ("offsets", C.c_void_p),
+        ("block_offsets", C.c_void_p),
+        ("offsets_are_int64", C.c_int32),
+        ("batch", C.c_int32),
+        ("total", C.c_int64),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("scale_rows", C.c_int64),
+    ]
+
+
 class GdpaNormBwdParams(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32),
@@ -191,6 +210,8 @@ def _load() -> C.CDLL:
     for fn in (lib.gdpa_layernorm_rows, lib.gdpa_rmsnorm_rows):
         fn.restype = C.c_int
         fn.argtypes = [C.POINTER(GdpaNormParams), C.c_void_p]
+    lib.gdpa_quantize_fp8_blockwise.restype = C.c_int
+    lib.gdpa_quantize_fp8_blockwise.argtypes = [C.POINTER(GdpaQuantParams), C.c_void_p]
     lib.gdpa_norm_rows_bwd.restype = C.c_int
     lib.gdpa_norm_rows_bwd.argtypes = [C.POINTER(GdpaNormBwdParams), C.c_void_p]
     lib.gdpa_fwd_fp8.restype = C.c_int

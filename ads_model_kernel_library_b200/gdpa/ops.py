@@ -615,34 +615,36 @@ def _ensemble(query, key, value, query_offset, key_offset, max_q, max_kv, scale,
 
 
 def quantize_fp8_blockwise(x: torch.Tensor, offsets: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Quantise a jagged ``[total, H, D]`` tensor to FP8 e4m3 with one fp32 scale per
-    (sequence-local 128-token block, head): ``scale = amax / 448`` over the block.
+    """Quantise a jagged ``[total, H, D]`` tensor (bf16 or fp32, CUDA) to FP8 e4m3 with one fp32 scale per
+    (sequence-local 128-token block, head): ``scale = max(amax / 448, 1e-12)`` over the block.
 
-    Returns ``(x_fp8, scales[num_blocks, H], block_offsets[B + 1])`` where block ``j`` of sequence
-    ``b`` is row ``block_offsets[b] + j`` of ``scales``.  Host-side utility (torch ops, one host
-    read of the offsets); it is the producer of the inputs of
-    :func:`generalized_dot_product_attention_fp8`.
+    Returns ``(x_fp8, scales[rows, H], block_offsets[B + 1])`` where block ``j`` of sequence ``b`` is row
+    ``block_offsets[b] + j`` of ``scales`` (``rows = total // 128 + B`` is an upper bound of the number of blocks;
+    rows past ``block_offsets[B]`` are zero).  Runs in the kernel library (``gdpa_quantize_fp8_blockwise``), without
+    a host synchronisation; it is the producer of the inputs of :func:`generalized_dot_product_attention_fp8`.
     """
-    off = offsets.to(torch.int64).cpu()
-    lens = off[1:] - off[:-1]
-    nblk = (lens + 127) // 128
-    blk_off = torch.zeros(off.numel(), dtype=torch.int64)
-    blk_off[1:] = torch.cumsum(nblk, 0)
+    if not x.is_cuda or x.dim() != 3 or x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("quantize_fp8_blockwise expects a CUDA [total, H, D] tensor of bf16 or fp32")
+    if offsets.dtype not in (torch.int32, torch.int64) or offsets.device != x.device or offsets.dim() != 1:
+        raise ValueError("offsets must be a 1-D int32 / int64 tensor on the device of x")
+    x = x.contiguous()
+    offsets = offsets.contiguous()
     total, H, D = x.shape
-    # block id of every token
-    tok_blk = torch.empty(total, dtype=torch.int64)
-    for b in range(lens.numel()):
-        s, e = int(off[b]), int(off[b + 1])
-        if e > s:
-            tok_blk[s:e] = int(blk_off[b]) + torch.arange(e - s) // 128
-    tok_blk = tok_blk.to(x.device)
-    nb = int(blk_off[-1])
-    amax = torch.zeros(max(nb, 1), H, dtype=torch.float32, device=x.device)
-    xa = x.float().abs().amax(dim=2)
-    amax.index_reduce_(0, tok_blk, xa, "amax", include_self=True)
-    scales = (amax / 448.0).clamp_min(1e-12)
-    x8 = (x.float() / scales[tok_blk].unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return x8, scales.contiguous(), blk_off.to(offsets.dtype).to(x.device)
+    batch = offsets.numel() - 1
+    rows = total // 128 + batch
+    with torch.cuda.device(x.device):
+        x8 = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        scales = torch.zeros(max(rows, 1), H, dtype=torch.float32, device=x.device)
+        blk_off = torch.empty(batch + 1, dtype=offsets.dtype, device=x.device)
+        p = _cabi.GdpaQuantParams()
+        p.struct_size = C.sizeof(_cabi.GdpaQuantParams)
+        p.in_is_fp32 = int(x.dtype == torch.float32)
+        p.x, p.x8, p.scales = x.data_ptr(), x8.data_ptr(), scales.data_ptr()
+        p.offsets, p.block_offsets = offsets.data_ptr(), blk_off.data_ptr()
+        p.offsets_are_int64 = int(offsets.dtype == torch.int64)
+        p.batch, p.total, p.heads, p.head_dim, p.scale_rows = batch, total, H, D, max(rows, 1)
+        _cabi.check(_cabi.lib.gdpa_quantize_fp8_blockwise(C.byref(p), _stream_ptr()), "gdpa_quantize_fp8_blockwise")
+    return x8, scales, blk_off
 
 
 def generalized_dot_product_attention_fp8(

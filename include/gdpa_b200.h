@@ -255,6 +255,31 @@ typedef struct GdpaNormBwdParams {
 
 int gdpa_norm_rows_bwd(const GdpaNormBwdParams* params, gdpa_stream_t stream);
 
+/* Producer of the FP8 inputs: quantises a jagged [total, heads, head_dim] tensor (bf16, or fp32 with
+ * in_is_fp32) to e4m3 with one fp32 scale per (sequence-local 128-token block, head):
+ * scale = max(amax / 448, 1e-12), value = e4m3(clamp(x / scale, -448, 448)).  Writes block_offsets
+ * ([batch + 1], the integer type of the offsets: exclusive prefix sum of ceil(len / 128)) and scales
+ * ([scale_rows, heads] fp32, scale_rows >= total / 128 + batch; rows past block_offsets[batch] are left
+ * untouched).  No counterpart in the reference, whose quantisation helper for its low-precision variant is
+ * missing from its tree (gdpa/src/interface.py:715-724 refers to it).  No host synchronisation. */
+typedef struct GdpaQuantParams {
+  uint32_t struct_size;   /* sizeof(GdpaQuantParams) */
+  int32_t in_is_fp32;
+  const void* x;
+  void* x8;               /* [total, heads, head_dim] e4m3 */
+  float* scales;
+  const void* offsets;    /* [batch + 1] */
+  void* block_offsets;    /* out: [batch + 1] */
+  int32_t offsets_are_int64;
+  int32_t batch;
+  int64_t total;
+  int32_t heads;
+  int32_t head_dim;       /* a multiple of 4 */
+  int64_t scale_rows;
+} GdpaQuantParams;
+
+int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* params, gdpa_stream_t stream);
+
 /* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16; every
  * activation, head_dim 128.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule

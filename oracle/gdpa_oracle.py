@@ -249,6 +249,30 @@ def gdpa_with_norms(query, key, value, query_offset, key_offset, activation="fas
     return x
 
 
+def quantize_fp8_blockwise(x: torch.Tensor, offsets: torch.Tensor):
+    """CPU restatement of this library's FP8 input format (no counterpart in the reference, whose quantisation
+    helper is missing from its tree): one fp32 scale per (sequence-local 128-token block, head),
+    ``scale = max(amax / 448, 1e-12)``, ``x8 = e4m3(clamp(x / scale, -448, 448))``.  Returns
+    ``(x8, scales[num_blocks, H], block_offsets[B + 1])``."""
+    off = offsets.to(torch.int64).cpu()
+    lens = (off[1:] - off[:-1]).clamp_min(0)
+    nblk = (lens + 127) // 128
+    blk_off = torch.zeros(off.numel(), dtype=torch.int64)
+    blk_off[1:] = torch.cumsum(nblk, 0)
+    total, H, D = x.shape
+    xf = x.detach().cpu().to(torch.float32)
+    scales = torch.zeros(int(blk_off[-1]), H, dtype=torch.float32)
+    x8 = torch.empty(total, H, D, dtype=torch.float8_e4m3fn)
+    for b in range(lens.numel()):
+        s, e = int(off[b]), int(off[b + 1])
+        for j, r0 in enumerate(range(s, e, 128)):
+            blk = xf[r0:min(r0 + 128, e)]
+            sc = (blk.abs().amax(dim=(0, 2)) / 448.0).clamp_min(1e-12)
+            scales[int(blk_off[b]) + j] = sc
+            x8[r0:min(r0 + 128, e)] = (blk / sc.view(1, H, 1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return x8, scales, blk_off.to(offsets.dtype)
+
+
 def gdpa_backward_formulas(
     query: torch.Tensor,
     key: torch.Tensor,

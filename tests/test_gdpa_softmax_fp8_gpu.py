@@ -162,3 +162,22 @@ def test_fp8_rejects_other_head_dims(G):
     x8, s, b = G.quantize_fp8_blockwise(x, qo)
     with pytest.raises((RuntimeError, NotImplementedError)):
         G.generalized_dot_product_attention_fp8(x8, x8, x8, s, s, s, b, b, qo, qo, 16, 16, activation="gelu_approx")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("off_dtype", [torch.int64, torch.int32])
+def test_fp8_block_quantiser_is_bit_exact_against_its_cpu_restatement(G, dtype, off_dtype):
+    """Byte work: the e4m3 codes, the scales and the block offsets must equal the CPU restatement bit for bit
+    (ragged lengths, an empty sequence, a length-1 sequence, zeros, values that saturate the block maximum)."""
+    lens = [128, 300, 0, 77, 1, 640, 129]
+    off = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=off_dtype)
+    g = torch.Generator().manual_seed(77)
+    x = (torch.randn(int(off[-1]), 3, 128, generator=g) * torch.logspace(-3, 2, 3).view(1, 3, 1)).to(dtype)
+    x[5:9] = 0
+    x8, sc, bo = G.quantize_fp8_blockwise(x.cuda(), off.cuda())
+    torch.cuda.synchronize()
+    r8, rsc, rbo = orc.quantize_fp8_blockwise(x, off)
+    nb = int(rbo[-1])
+    assert torch.equal(bo.cpu(), rbo)
+    assert torch.equal(sc.cpu()[:nb], rsc) and torch.count_nonzero(sc.cpu()[nb:]) == 0
+    assert torch.equal(x8.cpu().view(torch.uint8), r8.view(torch.uint8))

@@ -154,3 +154,25 @@ def test_norm_pipeline_oracle_follows_the_reference_test_formulation():
                                         eps=1e-5).view_as(g)
     torch.testing.assert_close(orc.gdpa_with_norms(q, k, v, off, off, "fast_gelu", None, fused_rms_norm=True), ref1,
                                atol=1e-6, rtol=1e-6)
+
+
+def test_fp8_block_format_restatement_properties():
+    """The CPU restatement of the FP8 input format: one scale per (128-token block of a sequence, head), codes
+    within e4m3's half-ulp of x / scale, the block maximum mapped to +-448."""
+    lens = [130, 0, 5, 256]
+    off = torch.tensor([0, 130, 130, 135, 391])
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(391, 2, 16, generator=g) * 3
+    x8, sc, bo = orc.quantize_fp8_blockwise(x, off)
+    assert bo.tolist() == [0, 2, 2, 3, 5] and sc.shape == (5, 2)
+    # block 1 of sequence 0 holds rows 128, 129 only
+    torch.testing.assert_close(sc[1], x[128:130].abs().amax(dim=(0, 2)) / 448.0)
+    deq = x8.float()
+    for b, (s, e) in enumerate(zip(off[:-1].tolist(), off[1:].tolist())):
+        for j, r0 in enumerate(range(s, e, 128)):
+            r1 = min(r0 + 128, e)
+            y = x[r0:r1] / sc[bo[b] + j].view(1, 2, 1)
+            assert float((deq[r0:r1] - y).abs().max()) <= 16.0 + 1e-3  # half an ulp at the top binade of e4m3
+            assert float(deq[r0:r1].abs().max()) == 448.0
+            rel = ((deq[r0:r1] - y).abs() / y.abs().clamp_min(2.0 ** -6))
+            assert float(rel.max()) <= 2.0 ** -4 + 1e-6
