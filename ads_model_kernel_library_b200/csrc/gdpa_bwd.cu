@@ -228,13 +228,20 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t p_phase = 0, ds_phase = 0, dqe_phase = 0, dkve_phase = 0;
         int tr = 0;  // trace: Q tiles seen so far (slot layout: tr * 32 + event, events 0-7 MMA, 8-12 element-wise, 13-16 reduce)
         const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff, sDs = smem_base + L::kDsOff;
+        // Descriptors of the operand buffers, built once; per MMA only the start address moves.
+        const uint64_t dK_k = umma_smem_desc_sw128(sK, 16, 1024), dV_k = umma_smem_desc_sw128(sV, 16, 1024);
+        const uint64_t dK_mn = umma_smem_desc_sw128(sK, L::kHalfBytes, 1024), dDs_mn = umma_smem_desc_sw128(sDs, L::kHalfBytes, 1024);
+        const uint64_t dQ0_k = umma_smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
+        const uint64_t dQ0_mn = umma_smem_desc_sw128(smem_base + L::kQOff, L::kHalfBytes, 1024);
+        const uint64_t dDo_k = umma_smem_desc_sw128(smem_base + L::kDoOff, 16, 1024);
+        const uint64_t dDo_mn = umma_smem_desc_sw128(smem_base + L::kDoOff, L::kHalfBytes, 1024);
         // A, B K-major over the head dim: D / 16 slices.
-        auto mma_kmajor_pair = [&](uint32_t d_col, uint32_t a_base, uint32_t b_base) {
+        auto mma_kmajor_pair = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = (kk >> 2) * L::kHalfBytes + (kk & 3) * 32;
-            umma_ss_f16(tmem_base + d_col, umma_smem_desc_sw128(a_base + off, 16, 1024),
-                        umma_smem_desc_sw128(b_base + off, 16, 1024), kIdescKK, kk > 0 ? 1u : 0u);
+            umma_ss_f16(tmem_base + d_col, umma_desc_advance(a_desc, off), umma_desc_advance(b_desc, off), kIdescKK,
+                        kk > 0 ? 1u : 0u);
           }
         };
         WorkWalker walker(n_items);
@@ -248,20 +255,19 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           GDPA_WAIT(BB_KV_FULL, kv_phase, ST_ROLE_MMA);
           kv_phase ^= 1u;
           for (int m = 0; m <= nq; ++m) {
-            const uint32_t sQ = smem_base + L::kQOff + st * L::kTileBytes;
-            const uint32_t sDo = smem_base + L::kDoOff;
+            const uint64_t dQ_k = umma_desc_advance(dQ0_k, st * L::kTileBytes);
             if (m < nq) {
               GDPA_TRACE(a, tr * 32 + 0);
               GDPA_WAIT(BB_Q_FULL + st, q_phase[st], ST_ROLE_MMA);
               q_phase[st] ^= 1u;
               tc_fence_after();
-              mma_kmajor_pair(kColS, sK, sQ);  // S^T = K Q_m^T
+              mma_kmajor_pair(kColS, dK_k, dQ_k);  // S^T = K Q_m^T
               tc_commit(bar_base + 8u * BB_S_FULL);
               GDPA_TRACE(a, tr * 32 + 1);
             }
             if (m > 0) {
               const uint32_t pst = st ^ 1u;
-              const uint32_t sQp = smem_base + L::kQOff + pst * L::kTileBytes;
+              const uint64_t dQp_mn = umma_desc_advance(dQ0_mn, pst * L::kTileBytes);
               GDPA_WAIT(BB_DS_FULL, ds_phase, ST_ROLE_MMA);
               ds_phase ^= 1u;
               tc_fence_after();
@@ -271,13 +277,13 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
                 umma_ts_f16(tmem_base + kColDK, tmem_base + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
-                            umma_smem_desc_sw128(sQp + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            umma_desc_advance(dQp_mn, kk * 2048), kIdescKM,
                             (m > 1 || kk > 0) ? 1u : 0u);
               // dQ_{m-1} = dS K : A = dS^T tile in shared memory read MN-major, B = K tile MN-major
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
-                umma_ss_f16(tmem_base + kColDP, umma_smem_desc_sw128(sDs + kk * 2048, L::kHalfBytes, 1024),
-                            umma_smem_desc_sw128(sK + kk * 2048, L::kHalfBytes, 1024), kIdescMM, kk > 0 ? 1u : 0u);
+                umma_ss_f16(tmem_base + kColDP, umma_desc_advance(dDs_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
+                            kIdescMM, kk > 0 ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DQ_FULL);
               tc_commit(bar_base + 8u * (BB_Q_EMPTY + pst));
               GDPA_TRACE(a, tr * 32 + 3);
@@ -289,7 +295,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               dqe_phase ^= 1u;
               tc_fence_after();
               GDPA_TRACE(a, tr * 32 + 4);
-              mma_kmajor_pair(kColDP, sV, sDo);  // dP^T = V dO_m^T
+              mma_kmajor_pair(kColDP, dV_k, dDo_k);  // dP^T = V dO_m^T
               tc_commit(bar_base + 8u * BB_DP_FULL);
               GDPA_TRACE(a, tr * 32 + 5);
               GDPA_WAIT(BB_P_FULL, p_phase, ST_ROLE_MMA);
@@ -304,7 +310,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
               for (int kk = 0; kk < kTile / 16; ++kk)
                 umma_ts_f16(tmem_base + kColDV, tmem_base + kColS + (kk >> 2) * 64 + (kk & 3) * 8,
-                            umma_smem_desc_sw128(sDo + kk * 2048, L::kHalfBytes, 1024), kIdescKM,
+                            umma_desc_advance(dDo_mn, kk * 2048), kIdescKM,
                             (m > 0 || kk > 0) ? 1u : 0u);
               tc_commit(bar_base + 8u * BB_DO_EMPTY);
               GDPA_TRACE(a, tr * 32 + 7);
