@@ -43,13 +43,20 @@ __device__ __forceinline__ long long load_offset(const void* p, int i, int is64)
 }
 
 // Cycle stamps for performance analysis: CTA 0 writes clock64() into slot `slot` of the trace buffer
-// when one was registered with gdpa_debug_set_trace(); otherwise a single predicated-off store.
+// when one was registered with gdpa_debug_set_trace(); otherwise a single predicated-off store.  Compiled in
+// where GDPA_ENABLE_TRACE is defined before this header is included: the forward kernel keeps its stamps (without
+// them it measured 3 % slower, an effect of instruction placement), the backward kernel has them only in builds
+// with -DGDPA_ENABLE_TRACE (its MMA-issuing thread is 6 % faster without the eight tests per Q tile).
 constexpr int kTraceSlots = 16384;
+#ifdef GDPA_ENABLE_TRACE
 #define GDPA_TRACE(args, slot)                                                                  \
   do {                                                                                          \
     if ((args).trace != nullptr && blockIdx.x == 0 && (slot) >= 0 && (slot) < kTraceSlots)     \
       (args).trace[(slot)] = clock64();                                                         \
   } while (0)
+#else
+#define GDPA_TRACE(args, slot) do { } while (0)
+#endif
 
 // One work item of a schedule, with the sequence geometry it refers to.
 struct Work {

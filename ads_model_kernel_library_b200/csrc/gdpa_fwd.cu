@@ -25,6 +25,9 @@
 // past the end of the tensor): S columns beyond the KV length are set to zero before the
 // activation (act(0) = 0 for every supported activation), Q rows beyond the Q length are
 // computed and never stored.
+#ifndef GDPA_ENABLE_TRACE
+#define GDPA_ENABLE_TRACE  // the forward keeps its cycle stamps, see GDPA_TRACE
+#endif
 #include "gdpa_common.cuh"
 #include "gdpa_launch.h"
 

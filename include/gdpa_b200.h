@@ -360,9 +360,9 @@ int64_t gdpa_launch_count(void);
 int gdpa_debug_wait_probe(int32_t* status, uint64_t limit_ns, gdpa_stream_t stream);
 
 /* Diagnostic hook for performance analysis: register a device buffer of 16384 int64 slots into which
- * CTA 0 of the forward / backward kernels writes SM cycle stamps at fixed points of its pipeline
- * (slot layout in csrc/gdpa_fwd.cu and csrc/gdpa_bwd.cu), or null to switch tracing off (default).
- * Process-wide; not meant for production use. */
+ * CTA 0 of the forward kernel (and of the backward kernel in a library built with -DGDPA_ENABLE_TRACE)
+ * writes SM cycle stamps at fixed points of its pipeline (slot layout in csrc/gdpa_fwd.cu and
+ * csrc/gdpa_bwd.cu), or null to switch tracing off (default).  Process-wide; not meant for production use. */
 void gdpa_debug_set_trace(void* device_buffer);
 
 /* Library version: major * 10000 + minor * 100 + patch. */
