@@ -173,7 +173,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp == kBwdLoadWarp) {
       // ---------------------------------------------------------------- TMA loader
       if (lane == 0) {
-        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase = 0, st = 0;
+        uint32_t kv_phase = 0, q_phase = 0 /* bit st = parity of Q stage st */, do_phase = 0, st = 0;
         WorkWalker walker(n_items);
         int idx;
         while (walker.next(idx)) {
@@ -198,8 +198,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           for (int m = 0; m < nq; ++m) {
             const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
-            GDPA_WAIT(BB_Q_EMPTY + st, q_phase[st] ^ 1u, ST_ROLE_LOAD);
-            q_phase[st] ^= 1u;
+            GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
+            q_phase ^= 1u << st;
             {
               const uint32_t bar = bar_base + 8u * (BB_Q_FULL + st);
               mbar_arrive_expect_tx(bar, L::kTileBytes);
@@ -224,7 +224,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp == kBwdMmaWarp) {
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
-        uint32_t kv_phase = 0, q_phase[2] = {0, 0}, do_phase = 0, st = 0;
+        uint32_t kv_phase = 0, q_phase = 0 /* bit st = parity of Q stage st */, do_phase = 0, st = 0;
         uint32_t p_phase = 0, ds_phase = 0, dqe_phase = 0, dkve_phase = 0;
         int tr = 0;  // trace: Q tiles seen so far (slot layout: tr * 32 + event, events 0-7 MMA, 8-12 element-wise, 13-16 reduce)
         const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff, sDs = smem_base + L::kDsOff;
@@ -258,8 +258,8 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint64_t dQ_k = umma_desc_advance(dQ0_k, st * L::kTileBytes);
             if (m < nq) {
               GDPA_TRACE(a, tr * 32 + 0);
-              GDPA_WAIT(BB_Q_FULL + st, q_phase[st], ST_ROLE_MMA);
-              q_phase[st] ^= 1u;
+              GDPA_WAIT(BB_Q_FULL + st, (q_phase >> st) & 1u, ST_ROLE_MMA);
+              q_phase ^= 1u << st;
               tc_fence_after();
               mma_kmajor_pair(kColS, dK_k, dQ_k);  // S^T = K Q_m^T
               tc_commit(bar_base + 8u * BB_S_FULL);
