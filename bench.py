@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 # DRAM bytes per Q token of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of
 # 48 sequences of the default workload, H=8, D=128; see profiles/gdpa_*_kernel_bf16_d128_gelu_small_case.md).
 # Traffic grows in proportion to the tokens, so a full launch is this figure times its Q tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.338e9 / 114351, "gdpa_fwd_kernel": 0.926e9 / 114351}
+NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.347e9 / 114351, "gdpa_fwd_kernel": 0.928e9 / 114351}
 
 METRIC = "gdpa_fwd_bwd_useful_tflops"
 UNIT = "TFLOP/s"
