@@ -335,6 +335,41 @@ int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* p, gdpa_stream_t stream) 
   return rc;
 }
 
+namespace {
+int run_mxfp8(const GdpaMxParams* p, int quantize, gdpa_stream_t stream) {
+  if (p == nullptr || p->struct_size != sizeof(GdpaMxParams)) return GDPA_ERR_BAD_ARG;
+  if (p->batch < 0 || p->total < 0 || p->heads <= 0 || p->heads > 65535 || p->head_dim <= 0 || p->head_dim % 32 != 0)
+    return GDPA_ERR_BAD_ARG;
+  if (p->scale_axis != 0 && p->scale_axis != 1) return GDPA_ERR_BAD_ARG;
+  if (p->offsets == nullptr || p->block_offsets == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->total > 0 && (p->x == nullptr || p->x8 == nullptr || p->sf == nullptr)) return GDPA_ERR_BAD_ARG;
+  if (p->sf_blocks < 0) return GDPA_ERR_BAD_ARG;
+  if (((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->sf)) & 3u) != 0)
+    return GDPA_ERR_MISALIGNED;
+  MxArgs a;
+  a.x = p->x;
+  a.x8 = p->x8;
+  a.sf = static_cast<uint8_t*>(p->sf);
+  a.offsets = p->offsets;
+  a.block_offsets = p->block_offsets;
+  a.off64 = p->offsets_are_int64;
+  a.batch = p->batch;
+  a.heads = p->heads;
+  a.head_dim = p->head_dim;
+  a.scale_axis = p->scale_axis;
+  a.sf_blocks = p->sf_blocks;
+  // the grid covers every block a batch of this size can have, clipped to the blocks the scale tensor holds
+  a.max_blocks = p->total > 0 ? p->total / kTile + p->batch : 0;
+  if (a.max_blocks > a.sf_blocks) a.max_blocks = a.sf_blocks;
+  const int rc = launch_mxfp8(a, quantize, p->x_is_fp32, static_cast<cudaStream_t>(stream));
+  if (rc == 0) g_launches.fetch_add(a.max_blocks > 0 ? 2 : 1);
+  return rc;
+}
+}  // namespace
+
+int gdpa_quantize_mxfp8(const GdpaMxParams* p, gdpa_stream_t stream) { return run_mxfp8(p, 1, stream); }
+int gdpa_dequantize_mxfp8(const GdpaMxParams* p, gdpa_stream_t stream) { return run_mxfp8(p, 0, stream); }
+
 int gdpa_norm_rows_bwd(const GdpaNormBwdParams* p, gdpa_stream_t stream) {
   if (p == nullptr || p->struct_size != sizeof(GdpaNormBwdParams)) return GDPA_ERR_BAD_ARG;
   if (p->mode < 0 || p->mode > 2 || p->rows < 0 || p->n <= 0 || p->n % 8 != 0) return GDPA_ERR_BAD_ARG;

@@ -71,6 +71,21 @@ struct QuantArgs {
   long long max_blocks;  // rows of `scales`: at least total / 128 + batch
 };
 
+struct MxArgs {
+  void* x;        // [total, H, D] bf16 or fp32: input of the quantiser, output of the de-quantiser
+  void* x8;       // [total, H, D] e4m3
+  uint8_t* sf;    // e8m0 scales in 512-byte atoms
+  const void* offsets;
+  void* block_offsets;
+  int off64;
+  int batch;
+  int heads;
+  int head_dim;
+  int scale_axis;       // 0: scales along the head dim (Q, K); 1: along the tokens (V)
+  long long sf_blocks;  // 128-row token blocks the scale tensor is laid out for (its head stride)
+  long long max_blocks; // grid bound: at least total / 128 + batch
+};
+
 struct NormBwdArgs {
   const __nv_bfloat16* dy;
   const __nv_bfloat16* dy_add;
@@ -145,6 +160,7 @@ int launch_dq_convert(const float* acc, __nv_bfloat16* dq, long long n, cudaStre
 int launch_layernorm_rows(const NormArgs& a, cudaStream_t stream);
 int launch_rmsnorm_rows(const NormArgs& a, cudaStream_t stream);
 int launch_quant_fp8(const QuantArgs& a, int in_is_fp32, cudaStream_t stream);
+int launch_mxfp8(const MxArgs& a, int quantize, int x_is_fp32, cudaStream_t stream);
 int launch_norm_rows_bwd(const NormBwdArgs& a, int mode, cudaStream_t stream);
 int launch_build_schedule(const SchedArgs& a, cudaStream_t stream);
 

@@ -29,6 +29,8 @@ EXPORTS = (
     "gdpa_rmsnorm_rows",
     "gdpa_norm_rows_bwd",
     "gdpa_quantize_fp8_blockwise",
+    "gdpa_quantize_mxfp8",
+    "gdpa_dequantize_mxfp8",
     "gdpa_bwd_workspace_bytes",
     "gdpa_bwd",
     "gdpa_strerror",
@@ -134,6 +136,26 @@ class GdpaQuantParams(C.Structure):
     ]
 
 
+class GdpaMxParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("x_is_fp32", C.c_int32),
+        ("x", C.c_void_p),
+        ("x8", C.c_void_p),
+        ("sf", C.c_void_p),
+        ("offsets", C.c_void_p),
+        ("block_offsets", C.c_void_p),
+        ("offsets_are_int64", C.c_int32),
+        ("batch", C.c_int32),
+        ("total", C.c_int64),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("scale_axis", C.c_int32),
+        ("reserved", C.c_int32),
+        ("sf_blocks", C.c_int64),
+    ]
+
+
 class GdpaNormBwdParams(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32),
@@ -212,6 +234,9 @@ def _load() -> C.CDLL:
         fn.argtypes = [C.POINTER(GdpaNormParams), C.c_void_p]
     lib.gdpa_quantize_fp8_blockwise.restype = C.c_int
     lib.gdpa_quantize_fp8_blockwise.argtypes = [C.POINTER(GdpaQuantParams), C.c_void_p]
+    for fn in (lib.gdpa_quantize_mxfp8, lib.gdpa_dequantize_mxfp8):
+        fn.restype = C.c_int
+        fn.argtypes = [C.POINTER(GdpaMxParams), C.c_void_p]
     lib.gdpa_norm_rows_bwd.restype = C.c_int
     lib.gdpa_norm_rows_bwd.argtypes = [C.POINTER(GdpaNormBwdParams), C.c_void_p]
     lib.gdpa_fwd_fp8.restype = C.c_int

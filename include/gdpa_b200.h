@@ -280,6 +280,46 @@ typedef struct GdpaQuantParams {
 
 int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* params, gdpa_stream_t stream);
 
+/* MXFP8 wire format of the reference's block-scaled variant (gdpa/src/interface.py:714-750,
+ * gdpa/src/flash_fwd_sm100.py:746-833): e4m3 elements in the jagged [total, heads, head_dim] shape plus one
+ * e8m0 scale (2^(code - 127)) per 32 elements along the contraction dimension.  Only the scale tensor is
+ * padded, every sequence to a multiple of 128 rows; block_offsets[b] * 128 is the reference's
+ * cu_seqlens_sf[b].  Scales live in 512-byte atoms of 128 rows x 4 scales, byte
+ * 16 * (row % 32) + 4 * (row / 32) + k for row `row` and 32-element block k of the atom:
+ *   scale_axis 0 (Q, K: scales along head_dim): rows are tokens, atom index
+ *     (head * sf_blocks + token_block) * ceil(head_dim / 128) + head_dim_atom;
+ *   scale_axis 1 (V: scales along the tokens): rows are head-dim indices, atom index
+ *     (head * ceil(head_dim / 128) + head_dim_atom) * sf_blocks + token_block.
+ * sf_blocks is the number of 128-row token blocks the scale tensor is laid out for: block_offsets[batch] for
+ * the reference's layout (known to a caller that has the sequence lengths on the host), or any upper bound such
+ * as total / 128 + batch.  gdpa_quantize_mxfp8 is the producer the reference refers to but does not contain
+ * (quantize_varlen_mxfp8_sf_only, gdpa/src/interface.py:715-724): code = exponent field of amax * (1 / 448) in
+ * fp32, plus one when its mantissa is not zero (the reference's rule for its P tile,
+ * gdpa/src/activation_utils.py:444-517), element = e4m3(x * 2^(127 - code)) to nearest even, saturating; scale
+ * bytes of rows past a sequence's end are zero.  gdpa_dequantize_mxfp8 is the exact inverse map into bf16 or fp32
+ * (every e4m3 value times a power of two is a bf16 number).  Both write block_offsets ([batch + 1], the integer
+ * type of the offsets).  head_dim a multiple of 32.  No host synchronisation. */
+typedef struct GdpaMxParams {
+  uint32_t struct_size;   /* sizeof(GdpaMxParams) */
+  int32_t x_is_fp32;      /* type of x: 0 bf16, 1 fp32 */
+  void* x;                /* [total, heads, head_dim]: in (quantise) / out (de-quantise) */
+  void* x8;               /* [total, heads, head_dim] e4m3: out / in */
+  void* sf;               /* heads * ceil(head_dim / 128) * sf_blocks * 512 bytes: out / in */
+  const void* offsets;    /* [batch + 1] */
+  void* block_offsets;    /* out: [batch + 1] */
+  int32_t offsets_are_int64;
+  int32_t batch;
+  int64_t total;
+  int32_t heads;
+  int32_t head_dim;
+  int32_t scale_axis;
+  int32_t reserved;
+  int64_t sf_blocks;
+} GdpaMxParams;
+
+int gdpa_quantize_mxfp8(const GdpaMxParams* params, gdpa_stream_t stream);
+int gdpa_dequantize_mxfp8(const GdpaMxParams* params, gdpa_stream_t stream);
+
 /* Low-precision forward: Q, K, V are FP8 e4m3 with the per-block fp32 scales above, O is bf16; every
  * activation, head_dim 128.
  * Mirrors the reference's FP8 variant (gdpa/src/flash_fwd_sm100.py:326-352, output dtype rule

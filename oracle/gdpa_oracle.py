@@ -273,6 +273,111 @@ def quantize_fp8_blockwise(x: torch.Tensor, offsets: torch.Tensor):
     return x8, scales, blk_off.to(offsets.dtype)
 
 
+def mx_e8m0_codes(amax: torch.Tensor) -> torch.Tensor:
+    """e8m0 code (uint8 held in int64) of blocks with absolute maxima ``amax`` (fp32) by the reference's round-up rule
+    for its P tile (gdpa/src/activation_utils.py:444-517): ``t = amax * (1 / 448)`` in fp32, the exponent field of
+    ``t``, plus one when the mantissa of ``t`` is not zero; 255 (the NaN code) is clamped to 254."""
+    t = (amax.to(torch.float32) * torch.tensor(1.0 / 448.0, dtype=torch.float32)).contiguous()
+    bits = t.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    e = (bits >> 23) & 0xFF
+    e = e + ((bits & 0x7FFFFF) != 0).to(torch.int64)
+    return e.clamp_max(254)
+
+
+def mx_scale_atom_byte(row: torch.Tensor, k: torch.Tensor) -> torch.Tensor:
+    """Byte inside a 512-byte scale atom (128 rows x 4 scales) of row ``row`` (0..127) and 32-element block ``k``
+    (0..3): the layout the reference builds with ``tile_atom_to_shape_SF`` (gdpa/src/flash_fwd_sm100.py:746-833)."""
+    return 16 * (row % 32) + 4 * (row // 32) + k
+
+
+def _mx_block_offsets(offsets: torch.Tensor) -> torch.Tensor:
+    off = offsets.to(torch.int64).cpu()
+    nblk = ((off[1:] - off[:-1]).clamp_min(0) + 127) // 128
+    blk_off = torch.zeros(off.numel(), dtype=torch.int64)
+    blk_off[1:] = torch.cumsum(nblk, 0)
+    return blk_off
+
+
+def quantize_mxfp8(x: torch.Tensor, offsets: torch.Tensor, scale_axis: int = 0, sf_blocks: Optional[int] = None):
+    """CPU restatement of the MXFP8 wire format of the reference's block-scaled variant (element tensor unpadded,
+    scale tensor padded per sequence to 128 rows: gdpa/src/interface.py:714-750): e4m3 elements, one e8m0 scale per
+    32 elements along the head dim (``scale_axis=0``: Q, K) or along the tokens (``scale_axis=1``: V).
+    Returns ``(x8, sf, cu_seqlens_sf)``: ``sf`` is a flat uint8 tensor of 512-byte atoms ordered
+    [head][token block][head-dim atom] (axis 0) or [head][head-dim atom][token block] (axis 1), ``sf_blocks`` token
+    blocks per head (default: exactly the blocks of the batch), zero where no element exists."""
+    off = offsets.to(torch.int64).cpu()
+    blk_off = _mx_block_offsets(offsets)
+    nblocks = int(blk_off[-1])
+    sf_blocks = nblocks if sf_blocks is None else int(sf_blocks)
+    total, H, D = x.shape
+    d_atoms = (D + 127) // 128
+    xf = x.detach().cpu().to(torch.float32)
+    x8 = torch.zeros(total, H, D, dtype=torch.float8_e4m3fn)
+    sf = torch.zeros(H * d_atoms * sf_blocks * 512, dtype=torch.uint8)
+    hs = torch.arange(H)
+    for b in range(off.numel() - 1):
+        s, e = int(off[b]), int(off[b + 1])
+        for j, r0 in enumerate(range(s, e, 128)):
+            g = int(blk_off[b]) + j
+            blk = xf[r0:min(r0 + 128, e)]  # [n, H, D]
+            n = blk.shape[0]
+            if scale_axis == 0:
+                v = blk.reshape(n, H, D // 32, 32)
+                codes = mx_e8m0_codes(v.abs().amax(dim=-1))  # [n, H, D/32]
+                inv = torch.pow(2.0, (127 - codes).to(torch.float64)).to(torch.float32)
+                q = (v * inv.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+                x8[r0:r0 + n] = q.reshape(n, H, D)
+                rows = torch.arange(n).view(n, 1, 1)
+                kb = torch.arange(D // 32).view(1, 1, -1)
+                atom = (hs.view(1, H, 1) * sf_blocks + g) * d_atoms + kb // 4
+                sf[(atom * 512 + mx_scale_atom_byte(rows, kb % 4)).reshape(-1)] = codes.reshape(-1).to(torch.uint8)
+            else:
+                pad = torch.zeros(128, H, D)
+                pad[:n] = blk
+                v = pad.reshape(4, 32, H, D)
+                codes = mx_e8m0_codes(v.abs().amax(dim=1))  # [4, H, D]
+                inv = torch.pow(2.0, (127 - codes).to(torch.float64)).to(torch.float32)
+                q = (v * inv.unsqueeze(1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(128, H, D)
+                x8[r0:r0 + n] = q[:n]
+                live = (torch.arange(4) * 32 < n).view(4, 1, 1).expand(4, H, D)  # 32-token blocks that hold a token
+                kb = torch.arange(4).view(4, 1, 1)
+                d = torch.arange(D).view(1, 1, D)
+                atom = (hs.view(1, H, 1) * d_atoms + d // 128) * sf_blocks + g
+                idx = (atom * 512 + mx_scale_atom_byte(d % 128, kb)).expand(4, H, D)
+                sf[idx[live]] = codes[live].to(torch.uint8)
+    return x8, sf, (blk_off * 128).to(torch.int32)
+
+
+def dequantize_mxfp8(x8: torch.Tensor, sf: torch.Tensor, offsets: torch.Tensor, scale_axis: int = 0,
+                     sf_blocks: Optional[int] = None) -> torch.Tensor:
+    """fp32 values of an MXFP8 tensor in the layout of :func:`quantize_mxfp8`: element * 2^(code - 127)."""
+    off = offsets.to(torch.int64).cpu()
+    blk_off = _mx_block_offsets(offsets)
+    total, H, D = x8.shape
+    d_atoms = (D + 127) // 128
+    sf_blocks = int(blk_off[-1]) if sf_blocks is None else int(sf_blocks)
+    sfl = sf.cpu().to(torch.int64)
+    xf = x8.cpu().to(torch.float32)
+    out = torch.zeros(total, H, D, dtype=torch.float32)
+    hs = torch.arange(H).view(1, H, 1)
+    d = torch.arange(D).view(1, 1, D)
+    for b in range(off.numel() - 1):
+        s, e = int(off[b]), int(off[b + 1])
+        if e <= s:
+            continue
+        t = torch.arange(e - s).view(-1, 1, 1)
+        g = int(blk_off[b]) + t // 128
+        if scale_axis == 0:
+            atom = (hs * sf_blocks + g) * d_atoms + d // 128
+            byte = mx_scale_atom_byte(t % 128, (d % 128) // 32)
+        else:
+            atom = (hs * d_atoms + d // 128) * sf_blocks + g
+            byte = mx_scale_atom_byte(d % 128, (t % 128) // 32)
+        codes = sfl[(atom * 512 + byte).reshape(-1)].reshape(e - s, H, D)
+        out[s:e] = (xf[s:e].to(torch.float64) * torch.pow(2.0, (codes - 127).to(torch.float64))).to(torch.float32)
+    return out
+
+
 def gdpa_backward_formulas(
     query: torch.Tensor,
     key: torch.Tensor,

@@ -176,3 +176,61 @@ def test_fp8_block_format_restatement_properties():
             assert float(deq[r0:r1].abs().max()) == 448.0
             rel = ((deq[r0:r1] - y).abs() / y.abs().clamp_min(2.0 ** -6))
             assert float(rel.max()) <= 2.0 ** -4 + 1e-6
+
+
+def test_mxfp8_scale_code_known_answers():
+    """e8m0 codes by the round-up rule of the reference's P quantisation (gdpa/src/activation_utils.py:444-517):
+    exponent field of amax / 448, plus one when the mantissa is not zero."""
+    amax = torch.tensor([448.0, 449.0, 1.0, 0.0, 224.0, 448.0 * 2.0 ** -20, 448.0 * 2.0 ** 10 * 1.5])
+    assert orc.mx_e8m0_codes(amax).tolist() == [127, 128, 119, 0, 126, 107, 138]
+    # the scaled block maximum never exceeds e4m3's largest value
+    g = torch.Generator().manual_seed(11)
+    a = torch.rand(4096, generator=g) * torch.pow(2.0, torch.randint(-40, 40, (4096,), generator=g).float())
+    scaled = a.double() * torch.pow(2.0, (127 - orc.mx_e8m0_codes(a)).double())
+    assert float(scaled.max()) <= 448.0 * (1 + 2.0 ** -22) and float(scaled.min()) > 224.0 * (1 - 2.0 ** -22)
+
+
+def test_mxfp8_scale_atom_layout():
+    """One 512-byte atom holds 128 rows x 4 scales, byte 16 * (row % 32) + 4 * (row / 32) + k: every byte once."""
+    rows = torch.arange(128).view(128, 1)
+    ks = torch.arange(4).view(1, 4)
+    idx = orc.mx_scale_atom_byte(rows, ks).reshape(-1)
+    assert sorted(idx.tolist()) == list(range(512))
+    assert int(orc.mx_scale_atom_byte(torch.tensor(33), torch.tensor(2))) == 16 + 4 + 2
+
+
+@pytest.mark.parametrize("axis", [0, 1])
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_mxfp8_restatement_round_trip(axis, D):
+    """Quantise -> de-quantise: every element within half an e4m3 ulp of its block's scale, scale rows padded
+    per sequence to 128, scale bytes of rows that do not exist zero, cu_seqlens_sf 128-aligned prefix sums."""
+    off = torch.tensor([0, 130, 130, 135, 391])
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(391, 2, D, generator=g) * torch.exp(2 * torch.randn(391, 2, 1, generator=g))
+    x8, sf, cu = orc.quantize_mxfp8(x, off, axis)
+    assert cu.tolist() == [0, 256, 256, 384, 640] and cu.dtype == torch.int32
+    d_atoms = (D + 127) // 128
+    assert sf.numel() == 2 * d_atoms * 5 * 512
+    y = orc.dequantize_mxfp8(x8, sf, off, axis)
+    # block maxima: along D (axis 0) per 32 elements of a row; along the tokens (axis 1) per 32 rows of a sequence
+    if axis == 0:
+        amax = x.reshape(391, 2, D // 32, 32).abs().amax(-1, keepdim=True).expand(-1, -1, -1, 32).reshape(391, 2, D)
+    else:
+        amax = torch.zeros_like(x)
+        for s, e in zip(off[:-1].tolist(), off[1:].tolist()):
+            for r0 in range(s, e, 32):
+                r1 = min(r0 + 32, e)
+                amax[r0:r1] = x[r0:r1].abs().amax(0, keepdim=True)
+    # the block maximum lands in [224, 448], where an e4m3 ulp is 32: error <= 16 / 224 of the block maximum
+    assert float(((y - x).abs() / amax.clamp_min(1e-30)).max()) <= 16.0 / 224.0 + 1e-6
+    rel = (y - x).abs() / x.abs().clamp_min(1e-30)
+    big = x.abs() >= amax * 2.0 ** -6  # normal range of the scaled e4m3 code
+    assert float(rel[big].max()) <= 2.0 ** -4 + 1e-6
+    # a larger layout (upper bound of blocks) holds the same scales at a different head stride
+    x8b, sfb, _ = orc.quantize_mxfp8(x, off, axis, sf_blocks=8)
+    assert torch.equal(x8b.view(torch.uint8), x8.view(torch.uint8))
+    torch.testing.assert_close(orc.dequantize_mxfp8(x8b, sfb, off, axis, sf_blocks=8), y, atol=0, rtol=0)
+    # rows 130..255 of sequence 0's second block do not exist: their scale bytes stay zero (axis 0)
+    if axis == 0:
+        atom = sf[(0 * 5 + 1) * d_atoms * 512:(0 * 5 + 1) * d_atoms * 512 + 512].view(32, 4, 4)
+        assert int(atom[2:, 0].sum()) == 0 and int(atom[:, 1:].sum()) == 0 and int(atom[:2, 0, :min(4, D // 32)].min()) > 0
