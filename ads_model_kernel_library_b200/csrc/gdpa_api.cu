@@ -338,13 +338,14 @@ int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* p, gdpa_stream_t stream) 
 namespace {
 int run_mxfp8(const GdpaMxParams* p, int quantize, gdpa_stream_t stream) {
   if (p == nullptr || p->struct_size != sizeof(GdpaMxParams)) return GDPA_ERR_BAD_ARG;
-  if (p->batch < 0 || p->total < 0 || p->heads <= 0 || p->heads > 65535 || p->head_dim <= 0 || p->head_dim % 32 != 0)
+  if (p->batch < 0 || p->total < 0 || p->heads <= 0 || p->heads > 65535 || p->head_dim <= 0 || p->head_dim % 32 != 0 ||
+      p->head_dim > 512)
     return GDPA_ERR_BAD_ARG;
   if (p->scale_axis != 0 && p->scale_axis != 1) return GDPA_ERR_BAD_ARG;
   if (p->offsets == nullptr || p->block_offsets == nullptr) return GDPA_ERR_BAD_ARG;
   if (p->total > 0 && (p->x == nullptr || p->x8 == nullptr || p->sf == nullptr)) return GDPA_ERR_BAD_ARG;
   if (p->sf_blocks < 0) return GDPA_ERR_BAD_ARG;
-  if (((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->sf)) & 3u) != 0)
+  if (((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->sf)) & 15u) != 0)
     return GDPA_ERR_MISALIGNED;
   MxArgs a;
   a.x = p->x;

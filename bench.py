@@ -175,6 +175,9 @@ def main():
     ap.add_argument("--norms", action="store_true",
                     help="time the forward of the GDPA-plus-norm pipeline (layer norm of Q, Q residual, RMS norm) "
                          "instead of the workload's own pass, and the two row-norm kernels against the HBM roofline")
+    ap.add_argument("--mxfp8", action="store_true",
+                    help="with --workload c4_fp8_softmax: feed the forward MXFP8 inputs (e4m3 + e8m0 scale per 32 elements); "
+                         "the three de-quantising passes are inside the timed step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-flops", type=float, default=None, help="useful FLOPs of the CPU sample per step of the reference arm")
@@ -208,7 +211,9 @@ def main():
     if args.activation:
         w.activation = args.activation
     strong = args.workload == "c5_zipf_sharded"
-    fp8 = args.workload == "c4_fp8_softmax"
+    fp8 = args.workload == "c4_fp8_softmax" and not args.mxfp8
+    mx = args.workload == "c4_fp8_softmax" and args.mxfp8
+    assert not args.mxfp8 or mx, "--mxfp8 goes with --workload c4_fp8_softmax"
     if args.norms:
         assert not fp8 and w.activation != "softmax", "--norms needs a bf16 workload with an element-wise activation"
         w.mode = "fwd"
@@ -233,6 +238,10 @@ def main():
             t["q8"], t["sq"], t["qb"] = G.quantize_fp8_blockwise(t["q"].float(), t["q_offsets"])
             t["k8"], t["sk"], t["kb"] = G.quantize_fp8_blockwise(t["k"].float(), t["kv_offsets"])
             t["v8"], t["sv"], t["vb"] = G.quantize_fp8_blockwise(t["v"].float(), t["kv_offsets"])
+        if mx:
+            t["q8"], t["sfq"], _ = G.quantize_varlen_mxfp8_sf_only(t["q"], t["q_offsets"], 0)
+            t["k8"], t["sfk"], _ = G.quantize_varlen_mxfp8_sf_only(t["k"], t["kv_offsets"], 0)
+            t["v8"], t["sfv"], _ = G.quantize_varlen_mxfp8_sf_only(t["v"], t["kv_offsets"], 1)
         batches.append(t)
     flops_rank = sum(useful_flops(b["lq"], b["lk"], w.heads, w.head_dim, w.mode) for b in batches)
     tokens_rank = sum(int(b["lq"].sum() + b["lk"].sum()) for b in batches)
@@ -245,6 +254,10 @@ def main():
                         G.gdpa_megakernel(b["q"], b["k"], b["v"], b["q_offsets"], b["kv_offsets"], b["max_q"], b["max_kv"],
                                           qk_scale=w.qk_scale, activation=w.activation, fused_layernorm=True,
                                           fused_q_residual_add=True, fused_rms_norm=True)
+                    elif mx:
+                        G.generalized_dot_product_attention_mxfp8(b["q8"], b["k8"], b["v8"], b["sfq"], b["sfk"], b["sfv"],
+                                                                  b["q_offsets"], b["kv_offsets"], b["max_q"], b["max_kv"],
+                                                                  qk_scale=w.qk_scale, activation=w.activation)
                     elif fp8:
                         G.generalized_dot_product_attention_fp8(b["q8"], b["k8"], b["v8"], b["sq"], b["sk"], b["sv"], b["qb"],
                                                                 b["kb"], b["q_offsets"], b["kv_offsets"], b["max_q"],
@@ -394,7 +407,7 @@ def main():
         line = {
             "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
-            "vs_baseline": None, "dtype": "fp8_e4m3" if fp8 else "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp8_e4m3" if fp8 else ("mxfp8 in, bf16 contraction" if mx else "bf16"), "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": int(sum(len(b["lq"]) for b in batches)), "heads": w.heads,
                        "head_dim": w.head_dim, "activation": w.activation, "pass": ("fwd+norms" if args.norms else "fwd") if fwd_only else "fwd+bwd",
                        "tokens_per_step": int(total_tokens), "useful_tflop_per_step": total_flops / 1e12,

@@ -298,7 +298,7 @@ int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* params, gdpa_stream_t str
  * gdpa/src/activation_utils.py:444-517), element = e4m3(x * 2^(127 - code)) to nearest even, saturating; scale
  * bytes of rows past a sequence's end are zero.  gdpa_dequantize_mxfp8 is the exact inverse map into bf16 or fp32
  * (every e4m3 value times a power of two is a bf16 number).  Both write block_offsets ([batch + 1], the integer
- * type of the offsets).  head_dim a multiple of 32.  No host synchronisation. */
+ * type of the offsets).  head_dim a multiple of 32, at most 512; x, x8 and sf 16-byte aligned.  No host synchronisation. */
 typedef struct GdpaMxParams {
   uint32_t struct_size;   /* sizeof(GdpaMxParams) */
   int32_t x_is_fp32;      /* type of x: 0 bf16, 1 fp32 */
