@@ -330,6 +330,7 @@ int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* p, gdpa_stream_t stream) 
   a.heads = p->heads;
   a.head_dim = p->head_dim;
   a.max_blocks = p->total > 0 ? p->total / kTile + p->batch : 0;
+  a.vec16 = p->head_dim % 16 == 0 && ((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x)) & 15u) == 0;
   const int rc = launch_quant_fp8(a, p->in_is_fp32, static_cast<cudaStream_t>(stream));
   if (rc == 0) g_launches.fetch_add(a.max_blocks > 0 ? 2 : 1);
   return rc;

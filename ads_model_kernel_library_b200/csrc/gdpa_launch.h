@@ -69,6 +69,7 @@ struct QuantArgs {
   int heads;
   int head_dim;
   long long max_blocks;  // rows of `scales`: at least total / 128 + batch
+  int vec16;             // head_dim a multiple of 16 and x, x8 16-byte aligned: 16-element vector accesses
 };
 
 struct MxArgs {

@@ -3,7 +3,7 @@
 // the block, value = e4m3(clamp(x / scale, -448, 448)) with round-to-nearest-even.  Block j of sequence b is row
 // block_offsets[b] + j of the scale tensor, block_offsets being the exclusive prefix sum of ceil(len / 128), which
 // the first kernel builds on the device (no host synchronisation).  HBM-bound byte work: one CTA of 128 threads
-// per (block, head), a thread per token row.
+// per (block, head), the 128 x D tile moved in 16-element pieces.
 //
 // Second format: MXFP8 (e4m3 elements, one e8m0 power-of-two scale per 32 elements along the contraction
 // dimension), the wire format of the reference's block-scaled variant (gdpa/src/flash_fwd_sm100.py:746-833,
@@ -77,53 +77,6 @@ __global__ void __launch_bounds__(kScanThreads) gdpa_block_offsets_kernel(const 
 
 __device__ __forceinline__ float load_elem(const float* p, long long i) { return p[i]; }
 __device__ __forceinline__ float load_elem(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
-
-template <typename T>
-__global__ void __launch_bounds__(kTile) gdpa_quant_fp8_kernel(const QuantArgs a) {
-  __shared__ float s_max[kTile / 32];
-  __shared__ float s_scale;
-  const long long g = blockIdx.x;  // block index over the batch
-  const int h = blockIdx.y;
-  if (g >= load_offset(a.block_offsets, a.batch, a.off64)) return;
-  // the sequence that owns block g: last b with block_offsets[b] <= g
-  int lo = 0, hi = a.batch;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (load_offset(a.block_offsets, mid, a.off64) <= g) lo = mid;
-    else hi = mid;
-  }
-  const int b = lo;
-  const long long seq_start = load_offset(a.offsets, b, a.off64), seq_end = load_offset(a.offsets, b + 1, a.off64);
-  const long long row = seq_start + (g - load_offset(a.block_offsets, b, a.off64)) * kTile + threadIdx.x;
-  const bool valid = row < seq_end;
-  const T* x = static_cast<const T*>(a.x);
-  const long long base = (row * a.heads + h) * static_cast<long long>(a.head_dim);
-  float amax = 0.f;
-  if (valid)
-    for (int d = 0; d < a.head_dim; ++d) amax = fmaxf(amax, fabsf(load_elem(x, base + d)));
-#pragma unroll
-  for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float m = s_max[0];
-    for (int i = 1; i < kTile / 32; ++i) m = fmaxf(m, s_max[i]);
-    const float scale = fmaxf(m / 448.f, 1e-12f);
-    s_scale = scale;
-    a.scales[g * a.heads + h] = scale;
-  }
-  __syncthreads();
-  if (!valid) return;
-  const float scale = s_scale;
-  uint32_t* out = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(a.x8) + base);
-  for (int d = 0; d < a.head_dim; d += 4) {
-    float v[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) v[e] = fminf(fmaxf(load_elem(x, base + d + e) / scale, -448.f), 448.f);
-    out[d >> 2] = pack_e4m3x4(v[0], v[1], v[2], v[3]);
-  }
-}
-
 
 // e8m0 code of a block with absolute maximum `amax`, and 2^(127 - code)
 __device__ __forceinline__ uint32_t mx_e8m0_of(float amax, float& inv_scale) {
@@ -330,6 +283,70 @@ __global__ void __launch_bounds__(kTile) gdpa_mxfp8_kernel(const MxArgs a) {
   if constexpr (QUANT) {
     __syncthreads();
     for (int da = 0; da < d_atoms; ++da) atom_words(da)[t] = reinterpret_cast<const uint32_t*>(s_sf[da])[t];
+  }
+}
+
+// One CTA of 128 threads per (128-token block, head): the 128 x D tile is read twice in 16-element pieces (8 lanes
+// cover 256 contiguous bytes of bf16), first for the block maximum, then (from L1 / L2) to quantise.
+template <typename T>
+__global__ void __launch_bounds__(kTile) gdpa_quant_fp8_kernel(const QuantArgs a) {
+  __shared__ float s_max[kTile / 32];
+  __shared__ float s_scale;
+  const long long g = blockIdx.x;  // block index over the batch
+  const int h = blockIdx.y;
+  if (g >= load_offset(a.block_offsets, a.batch, a.off64)) return;
+  const int b = owner_of_block(a.block_offsets, a.off64, a.batch, g);
+  const long long seq_end = load_offset(a.offsets, b + 1, a.off64);
+  const long long row0 = load_offset(a.offsets, b, a.off64) + (g - load_offset(a.block_offsets, b, a.off64)) * kTile;
+  const int nrows = static_cast<int>(min(static_cast<long long>(kTile), seq_end - row0));
+  const int t = threadIdx.x;
+  const int D = a.head_dim;
+  const T* x = static_cast<const T*>(a.x);
+  uint8_t* x8 = static_cast<uint8_t*>(a.x8);
+  auto elem_base = [&](int row) { return ((row0 + row) * a.heads + h) * static_cast<long long>(D); };
+  float amax = 0.f;
+  if (a.vec16) {
+    const int cpr = D / 16, limit = nrows * cpr;
+    for (int idx = t; idx < limit; idx += kTile) {
+      float v[16];
+      load16(x + elem_base(idx / cpr) + (idx % cpr) * 16, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+  } else if (t < nrows) {
+    for (int d = 0; d < D; ++d) amax = fmaxf(amax, fabsf(load_elem(x, elem_base(t) + d)));
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+  if ((t & 31) == 0) s_max[t >> 5] = amax;
+  __syncthreads();
+  if (t == 0) {
+    float m = s_max[0];
+    for (int i = 1; i < kTile / 32; ++i) m = fmaxf(m, s_max[i]);
+    const float scale = fmaxf(m / 448.f, 1e-12f);
+    s_scale = scale;
+    a.scales[g * a.heads + h] = scale;
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  if (a.vec16) {
+    const int cpr = D / 16, limit = nrows * cpr;
+    for (int idx = t; idx < limit; idx += kTile) {
+      const long long at = elem_base(idx / cpr) + (idx % cpr) * 16;
+      float v[16];
+      load16(x + at, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = fminf(fmaxf(v[i] / scale, -448.f), 448.f);
+      *reinterpret_cast<uint4*>(x8 + at) = pack_e4m3x16(v);
+    }
+  } else if (t < nrows) {
+    uint32_t* out = reinterpret_cast<uint32_t*>(x8 + elem_base(t));
+    for (int d = 0; d < D; d += 4) {
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = fminf(fmaxf(load_elem(x, elem_base(t) + d + e) / scale, -448.f), 448.f);
+      out[d >> 2] = pack_e4m3x4(v[0], v[1], v[2], v[3]);
+    }
   }
 }
 
