@@ -65,6 +65,25 @@ def test_argument_checks_before_any_cuda_call(cabi):
     assert b"head_dim" in cabi.lib.gdpa_strerror(2)
 
 
+def test_mxfp8_entry_points_check_arguments_before_any_cuda_call(cabi):
+    for fn in (cabi.lib.gdpa_quantize_mxfp8, cabi.lib.gdpa_dequantize_mxfp8):
+        p = cabi.GdpaMxParams()
+        p.struct_size = 8
+        assert fn(C.byref(p), None) == 1  # struct layout disagrees
+        p.struct_size = C.sizeof(cabi.GdpaMxParams)
+        p.heads, p.head_dim, p.batch, p.total = 2, 48, 1, 4
+        p.offsets = p.block_offsets = 16
+        assert fn(C.byref(p), None) == 1  # head_dim not a multiple of 32
+        p.head_dim = 1024
+        assert fn(C.byref(p), None) == 1  # more than four scale atoms per row
+        p.head_dim, p.scale_axis = 128, 2
+        assert fn(C.byref(p), None) == 1  # unknown scale axis
+        p.scale_axis = 1
+        assert fn(C.byref(p), None) == 1  # null data with total > 0
+        p.x, p.x8, p.sf, p.sf_blocks = 16, 32, 52, 1
+        assert fn(C.byref(p), None) == 5  # GDPA_ERR_MISALIGNED: scale tensor not 16-byte aligned
+
+
 def test_schedule_and_workspace_sizes(cabi):
     lib = cabi.lib
     assert lib.gdpa_schedule_bytes(0, 1000, 4, 2) == 16 + 16 * 2 * (1000 // 256 + 4)
