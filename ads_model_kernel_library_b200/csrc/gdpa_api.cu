@@ -106,6 +106,7 @@ int check_common(const P* p) {
   if (p->window_plus_one < 0 || p->window_plus_one > (1 << 29)) return GDPA_ERR_BAD_ARG;
   if (p->head_dim != 64 && p->head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM;
   if (p->q_offsets == nullptr || p->kv_offsets == nullptr || p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
+  if ((p->offsets_are_int64 & ~(GDPA_OFFSETS_INT64 | GDPA_OFFSETS_PAIRS)) != 0) return GDPA_ERR_BAD_ARG;
   // TMA coordinates are 32-bit row indices.
   if (p->total_q >= (1ll << 31) || p->total_kv >= (1ll << 31)) return GDPA_ERR_BAD_ARG;
   return GDPA_OK;
@@ -168,6 +169,8 @@ int gdpa_build_schedule(const GdpaSchedParams* p, gdpa_stream_t stream) {
   if (p->batch > 0 && (p->q_offsets == nullptr || p->kv_offsets == nullptr)) return GDPA_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(p->schedule) & 15u) != 0) return GDPA_ERR_MISALIGNED;
   if (p->schedule_bytes < kSchedHeaderInts * 4 + 16) return GDPA_ERR_CAPACITY;
+  if ((p->offsets_are_int64 & ~(GDPA_OFFSETS_INT64 | GDPA_OFFSETS_PAIRS)) != 0) return GDPA_ERR_BAD_ARG;
+  if ((p->offsets_are_int64 & GDPA_OFFSETS_PAIRS) != 0 && p->kv_seq_index != nullptr) return GDPA_ERR_BAD_ARG;
   SchedArgs a;
   a.q_off = p->q_offsets;
   a.kv_off = p->kv_offsets;
@@ -201,6 +204,7 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   const int kv_heads = p->kv_heads > 0 ? p->kv_heads : p->heads;
   if (p->heads % kv_heads != 0) return GDPA_ERR_BAD_ARG;
   if ((p->residual != nullptr || p->row_sumsq != nullptr) && (fp8 || act == ACT_SOFTMAX)) return GDPA_ERR_BAD_ARG;
+  if ((p->offsets_are_int64 & GDPA_OFFSETS_PAIRS) != 0 && (fp8 || p->kv_seq_index != nullptr)) return GDPA_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(p->residual) & 15u) != 0) return GDPA_ERR_MISALIGNED;
   DeviceInfo di;
   rc = device_info(&di);
@@ -430,6 +434,9 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   if (p->k == nullptr || p->v == nullptr || p->dk == nullptr || p->dv == nullptr) return GDPA_ERR_BAD_ARG;
   if (((reinterpret_cast<uintptr_t>(p->dk) | reinterpret_cast<uintptr_t>(p->dv) | reinterpret_cast<uintptr_t>(p->dq)) & 15u) != 0)
     return GDPA_ERR_MISALIGNED;
+  const bool pairs = (p->offsets_are_int64 & GDPA_OFFSETS_PAIRS) != 0;
+  if (pairs && p->dkv_accum == nullptr) return GDPA_ERR_BAD_ARG;
+  if (pairs && (reinterpret_cast<uintptr_t>(p->dkv_accum) & 15u) != 0) return GDPA_ERR_MISALIGNED;
   DeviceInfo di;
   rc = device_info(&di);
   if (rc != GDPA_OK) return rc;
@@ -470,9 +477,12 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.lse = p->lse;
   l.args.dpsum = p->dpsum;
   l.args.total_q = p->total_q;
+  l.args.dk_acc = pairs ? static_cast<float*>(p->dkv_accum) : nullptr;
+  l.args.dv_acc = pairs ? static_cast<float*>(p->dkv_accum) + elems_kv : nullptr;
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+  if (pairs && cudaMemsetAsync(p->dkv_accum, 0, 2 * elems_kv * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
   if (act == ACT_SOFTMAX) {
     rc = launch_dpsum(static_cast<const __nv_bfloat16*>(p->d_o), static_cast<const __nv_bfloat16*>(p->o), p->dpsum,
                       p->total_q, p->heads, p->head_dim, st);
@@ -486,6 +496,11 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   rc = launch_dq_convert(static_cast<const float*>(p->dq_accum), static_cast<__nv_bfloat16*>(p->dq),
                          static_cast<long long>(elems_q), st);
   if (rc == 0) g_launches.fetch_add(2);
+  if (rc == 0 && pairs) {
+    rc = launch_dq_convert(l.args.dk_acc, static_cast<__nv_bfloat16*>(p->dk), static_cast<long long>(elems_kv), st);
+    if (rc == 0) rc = launch_dq_convert(l.args.dv_acc, static_cast<__nv_bfloat16*>(p->dv), static_cast<long long>(elems_kv), st);
+    if (rc == 0) g_launches.fetch_add(2);
+  }
   return rc;
 }
 

@@ -123,7 +123,8 @@ struct BwdSmem {
     if (!__all_sync(0xffffffffu, ok_)) goto role_done;                                                              \
   }
 
-template <int D, int ACT>
+// ACC: dK / dV tiles are added into fp32 accumulators instead of stored (K / V rows shared between sequences).
+template <int D, int ACT, bool ACC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -530,7 +531,17 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint32_t r[32];
           tmem_ld32(tcol + c * 32, r);
           tmem_wait_ld();
-          if (row_valid) {
+          if constexpr (ACC) {
+            // K / V rows shared between sequences (start / end offsets): every owner adds into fp32 accumulators
+            if (row_valid) {
+              float* acc_row = (t == 0 ? a.dv_acc : a.dk_acc) + (dst_row - (t == 0 ? a.dv : a.dk)) + c * 32;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                atomicAdd(reinterpret_cast<float4*>(acc_row) + j,
+                          make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                      __uint_as_float(r[4 * j + 3])));
+            }
+          } else if (row_valid) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
@@ -660,14 +671,19 @@ __global__ void __launch_bounds__(256) gdpa_dpsum_kernel(const __nv_bfloat16* __
   }
 }
 
-template <int D, int ACT>
-int launch_bwd_inst(const BwdLaunch& l) {
+template <int D, int ACT, bool ACC>
+int launch_bwd_acc(const BwdLaunch& l) {
   using L = BwdSmem<D>;
-  auto kernel = gdpa_bwd_kernel<D, ACT>;
+  auto kernel = gdpa_bwd_kernel<D, ACT, ACC>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
   kernel<<<l.grid, kBwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_do, l.tm_dq, l.args);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
+}
+
+template <int D, int ACT>
+int launch_bwd_inst(const BwdLaunch& l) {
+  return l.args.dk_acc != nullptr ? launch_bwd_acc<D, ACT, true>(l) : launch_bwd_acc<D, ACT, false>(l);
 }
 
 template <int D>

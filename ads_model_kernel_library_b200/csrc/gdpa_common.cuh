@@ -38,8 +38,18 @@ __host__ __device__ inline int act_class_from_id(int id) {
   }
 }
 
-__device__ __forceinline__ long long load_offset(const void* p, int i, int is64) {
-  return is64 ? static_cast<const long long*>(p)[i] : static_cast<long long>(static_cast<const int*>(p)[i]);
+// Offset flags: bit 0 = 64-bit entries; bit 1 = the array holds [start, end] pairs, two entries per sequence (the
+// reference's use_start_end_offsets, gdpa/triton/triton_generalized_dot_product_attention.py:943-946, :4270-4274:
+// sequences may then share or overlap K / V rows), instead of batch + 1 prefix sums.
+constexpr int kOffsets64 = 1, kOffsetsPairs = 2;
+__device__ __forceinline__ long long load_offset(const void* p, int i, int flags) {
+  return (flags & kOffsets64) ? static_cast<const long long*>(p)[i] : static_cast<long long>(static_cast<const int*>(p)[i]);
+}
+// first row and row past the end of sequence b
+__device__ __forceinline__ void seq_bounds(const void* p, int b, int flags, long long& start, long long& end) {
+  const int i = (flags & kOffsetsPairs) ? 2 * b : b;
+  start = load_offset(p, i, flags);
+  end = load_offset(p, i + 1, flags);
 }
 
 // Cycle stamps for performance analysis: CTA 0 writes clock64() into slot `slot` of the trace buffer
@@ -76,10 +86,11 @@ __device__ __forceinline__ Work load_work(const int* sched, int idx, const void*
   w.h = it.y;
   w.blk = it.z;
   const int kb = kv_index != nullptr ? static_cast<int>(load_offset(kv_index, w.b, is64)) : w.b;
-  w.q_start = load_offset(q_off, w.b, is64);
-  w.kv_start = load_offset(kv_off, kb, is64);
-  long long lq = load_offset(q_off, w.b + 1, is64) - w.q_start;
-  long long lkv = load_offset(kv_off, kb + 1, is64) - w.kv_start;
+  long long q_end, kv_end;
+  seq_bounds(q_off, w.b, is64, w.q_start, q_end);
+  seq_bounds(kv_off, kb, is64, w.kv_start, kv_end);
+  long long lq = q_end - w.q_start;
+  long long lkv = kv_end - w.kv_start;
   w.lq = static_cast<int>(lq < max_q ? lq : max_q);
   w.lkv = static_cast<int>(lkv < max_kv ? lkv : max_kv);
   if (w.lq < 0) w.lq = 0;

@@ -128,6 +128,8 @@ struct BwdArgs {
   int q_heads;         // query heads; `heads` above is the number of K / V heads (the work items' heads)
   int kv_group;        // q_heads / heads: a work item walks the Q tiles of every query head of its group
   int window;          // band |q - kv| <= window of sequence-local positions; -1 = none
+  float* dk_acc;       // start / end offsets: fp32 accumulators the dK / dV tiles are added into (else null)
+  float* dv_acc;
 };
 
 struct BwdLaunch {

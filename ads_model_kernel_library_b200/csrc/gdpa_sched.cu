@@ -16,9 +16,12 @@ constexpr int kSchedThreads = 1024;
 constexpr int kBins = 4096;
 
 __device__ __forceinline__ void seq_geometry(const SchedArgs& a, int b, int& nblk, int& weight) {
-  long long lq = load_offset(a.q_off, b + 1, a.off64) - load_offset(a.q_off, b, a.off64);
+  long long s0, e0;
+  seq_bounds(a.q_off, b, a.off64, s0, e0);
+  long long lq = e0 - s0;
   const int kb = a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, b, a.off64)) : b;
-  long long lkv = load_offset(a.kv_off, kb + 1, a.off64) - load_offset(a.kv_off, kb, a.off64);
+  seq_bounds(a.kv_off, kb, a.off64, s0, e0);
+  long long lkv = e0 - s0;
   lq = lq < 0 ? 0 : (lq < a.max_q ? lq : a.max_q);
   lkv = lkv < 0 ? 0 : (lkv < a.max_kv ? lkv : a.max_kv);
   const int nq = static_cast<int>((lq + kTile - 1) / kTile);

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libgdpa_b200.so")
 GDPA_OK = 0
 GDPA_DTYPE_BF16 = 0
 GDPA_DTYPE_FP8_E4M3 = 1
+GDPA_OFFSETS_INT64, GDPA_OFFSETS_PAIRS = 1, 2
 GDPA_SCHED_FWD = 0
 GDPA_SCHED_BWD = 1
 GDPA_ACT_SOFTMAX = 100
@@ -211,6 +212,7 @@ class GdpaBwdParams(C.Structure):
         ("q_strides", C.c_int64 * 2),
         ("k_strides", C.c_int64 * 2),
         ("v_strides", C.c_int64 * 2),
+        ("dkv_accum", C.c_void_p),
     ]
 
 

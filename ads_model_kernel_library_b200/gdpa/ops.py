@@ -77,7 +77,7 @@ def _stream_ptr() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False) -> Tuple[int, int, int]:
+def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False, start_end: bool = False) -> Tuple[int, int, int]:
     for name, t in (("query", q), ("key", k), ("value", v)):
         if t.dim() != 3:
             raise ValueError(f"{name} must be [total_tokens, H, D], got {tuple(t.shape)}")
@@ -109,11 +109,19 @@ def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False) -> Tuple[int,
             raise ValueError(f"{name} must be contiguous")
     if qo.dtype != ko.dtype or (qo.numel() != ko.numel() and not shared_kv):
         raise ValueError("query_offset and key_offset must have the same length and dtype")
+    if start_end:
+        if qo.numel() % 2 != 0:
+            raise ValueError("start / end offsets hold two entries per sequence")
+        return qo.numel() // 2, H, D
     return qo.numel() - 1, H, D
 
 
+def _offset_flags(offsets: torch.Tensor, start_end: bool = False) -> int:
+    return (_cabi.GDPA_OFFSETS_INT64 if offsets.dtype == torch.int64 else 0) | (_cabi.GDPA_OFFSETS_PAIRS if start_end else 0)
+
+
 def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, max_q: int, max_kv: int,
-                    kv_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    kv_index: Optional[torch.Tensor] = None, start_end: bool = False) -> torch.Tensor:
     nbytes = _cabi.lib.gdpa_schedule_bytes(mode, total_rows, batch, heads)
     sched = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=qo.device)
     p = _cabi.GdpaSchedParams()
@@ -121,7 +129,7 @@ def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, 
     p.mode = mode
     p.q_offsets = qo.data_ptr()
     p.kv_offsets = ko.data_ptr()
-    p.offsets_are_int64 = int(qo.dtype == torch.int64)
+    p.offsets_are_int64 = _offset_flags(qo, start_end)
     p.batch = batch
     p.heads = heads
     p.max_seq_len_q = max_q
@@ -167,16 +175,20 @@ def _gdpa_forward_op(
     qk_scale: float,
     activation: int,
     window_size: int = -1,
+    start_end_offsets: bool = False,
 ) -> torch.Tensor:
-    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16, start_end=start_end_offsets)
     with torch.cuda.device(query.device):
         o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         if query.shape[0] == 0 or batch == 0:
             return o
-        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
-                                max_seq_len_q, max_seq_len_kv)
+        # with start / end offsets the longest sequence is not bounded by the rows of the tensors
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H,
+                                batch * max_seq_len_q if start_end_offsets else query.shape[0],
+                                max_seq_len_q, max_seq_len_kv, start_end=start_end_offsets)
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
+        p.offsets_are_int64 = _offset_flags(query_offset, start_end_offsets)
         p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
@@ -184,7 +196,8 @@ def _gdpa_forward_op(
 
 
 @_gdpa_forward_op.register_fake
-def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, window_size=-1):
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, window_size=-1,
+      start_end_offsets=False):
     return query.new_empty(query.shape)
 
 
@@ -203,8 +216,9 @@ def _gdpa_backward_op(
     out: Optional[torch.Tensor] = None,
     lse: Optional[torch.Tensor] = None,
     window_size: int = -1,
+    start_end_offsets: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16, start_end=start_end_offsets)
     if activation == SOFTMAX_ID and (out is None or lse is None):
         raise ValueError("the softmax backward needs the forward output and its log-sum-exp")
     if do.shape != query.shape or do.dtype != query.dtype:
@@ -218,8 +232,9 @@ def _gdpa_backward_op(
             return dq, dk, dv
         # backward work items are (sequence, K/V head, KV tile); with grouped-query attention one item
         # walks the Q tiles of every query head of its group
-        sched = _build_schedule(_cabi.GDPA_SCHED_BWD, query_offset, key_offset, batch, key.shape[1], key.shape[0],
-                                max_seq_len_q, max_seq_len_kv)
+        sched = _build_schedule(_cabi.GDPA_SCHED_BWD, query_offset, key_offset, batch, key.shape[1],
+                                batch * max_seq_len_kv if start_end_offsets else key.shape[0],
+                                max_seq_len_q, max_seq_len_kv, start_end=start_end_offsets)
         acc_bytes = _cabi.lib.gdpa_bwd_workspace_bytes(query.shape[0], H, D)
         dq_accum = torch.empty(max(acc_bytes // 4, 1), dtype=torch.float32, device=query.device)
         p = _cabi.GdpaBwdParams()
@@ -228,13 +243,16 @@ def _gdpa_backward_op(
         p.q, p.k, p.v, p.d_o = query.data_ptr(), key.data_ptr(), value.data_ptr(), do.data_ptr()
         p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         p.q_offsets, p.kv_offsets = query_offset.data_ptr(), key_offset.data_ptr()
-        p.offsets_are_int64 = int(query_offset.dtype == torch.int64)
+        p.offsets_are_int64 = _offset_flags(query_offset, start_end_offsets)
         p.batch = batch
         p.total_q, p.total_kv = query.shape[0], key.shape[0]
         p.heads, p.head_dim = H, D
         for field, t in (("q_strides", query), ("k_strides", key), ("v_strides", value)):
             getattr(p, field)[0], getattr(p, field)[1] = t.stride(0), t.stride(1)
         p.kv_heads = key.shape[1]
+        if start_end_offsets:  # K / V rows may belong to several sequences: dK, dV are summed in fp32
+            dkv_accum = torch.empty(max(2 * key.numel(), 1), dtype=torch.float32, device=query.device)
+            p.dkv_accum = dkv_accum.data_ptr()
         p.max_seq_len_q, p.max_seq_len_kv = max_seq_len_q, max_seq_len_kv
         p.activation = activation
         p.qk_scale = qk_scale
@@ -253,23 +271,24 @@ def _gdpa_backward_op(
 
 @_gdpa_backward_op.register_fake
 def _(do, query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, activation, out=None,
-      lse=None, window_size=-1):
+      lse=None, window_size=-1, start_end_offsets=False):
     return query.new_empty(query.shape), key.new_empty(key.shape), value.new_empty(value.shape)
 
 
 def _setup_context(ctx, inputs, output):
-    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, activation, window_size = inputs
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, activation, window_size, start_end = inputs
     ctx.save_for_backward(query, key, value, query_offset, key_offset)
     ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation, ctx.window_size = max_q, max_kv, qk_scale, activation, window_size
+    ctx.start_end = start_end
 
 
 def _backward(ctx, do):
     query, key, value, query_offset, key_offset = ctx.saved_tensors
     dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
         do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.activation,
-        None, None, ctx.window_size
+        None, None, ctx.window_size, ctx.start_end
     )
-    return dq, dk, dv, None, None, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
 _gdpa_forward_op.register_autograd(_backward, setup_context=_setup_context)
@@ -478,7 +497,10 @@ def generalized_dot_product_attention(
     sequence, so that many Q sequences share one KV sequence) is supported for the forward only;
     ``window_size=W`` keeps only pairs of sequence-local positions with ``|q - kv| <= W``;
     ``broadcast_q`` (one Q sequence shared by the whole batch) and ``ensemble_activation_list`` (one
-    activation id per head) are composed on the host from calls of the same kernels.  Every other
+    activation id per head) are composed on the host from calls of the same kernels;
+    ``use_start_end_offsets`` (offsets ``[start_0, end_0, start_1, end_1, ...]``: sequences may share or overlap
+    K / V rows; dK and dV are then summed in fp32 over the sequences that read a row) is supported forward and
+    backward for the element-wise activations.  Every other
     non-default option raises, as the reference does for masks and causality (:3138-3139).
     """
     if attn_mask is not None:
@@ -500,12 +522,30 @@ def generalized_dot_product_attention(
     for name, val in unsupported.items():
         if val is not None:
             raise NotImplementedError(f"{name} is not supported by this implementation")
-    if use_start_end_offsets:
-        raise NotImplementedError("use_start_end_offsets is not supported by this implementation")
-    if output_offset is not None and not broadcast_q:
-        raise NotImplementedError("output_offset is supported together with broadcast_q only")
     act_id = activation_string_to_int(activation)
     scale = 1.0 if qk_scale is None else float(qk_scale)
+    if use_start_end_offsets:
+        # reference: :3142-3146 (no packed layouts, no broadcast_q, total_num_objects required), output rows of
+        # sequence b at query_offset[2 b] (:3156-3157, :625), output of total_num_objects rows (:3015-3024)
+        if key is None or value is None or broadcast_q:
+            raise ValueError("fused_qkv/fused_kv/broadcast_q not supported with start/end offsets")
+        if total_num_objects is None:
+            raise ValueError("total_num_objects must be provided")
+        if int(total_num_objects) != query.shape[0]:
+            raise NotImplementedError("total_num_objects must equal the number of query rows")
+        if ad_to_request_offset is not None or ensemble_activation_list or output_offset is not None:
+            raise NotImplementedError("start/end offsets together with ad_to_request_offset, ensemble_activation_list or "
+                                      "output_offset are not supported")
+        if act_id == SOFTMAX_ID:
+            raise NotImplementedError("start/end offsets are not supported for the softmax variant")
+        window = -1 if window_size is None else int(window_size)
+        if window_size is not None and window < 0:
+            raise ValueError("window_size must be non-negative")
+        return torch.ops.gdpa.generalized_dot_product_attention(
+            expect_contiguous(query), key, value, query_offset.contiguous(), key_offset.contiguous(), int(max_seq_len_q),
+            int(max_seq_len_kv), scale, act_id, window, True)
+    if output_offset is not None and not broadcast_q:
+        raise NotImplementedError("output_offset is supported together with broadcast_q only")
     # Packed layouts of the reference (:605-622): query = [T, H, 3D] with key = value = None, or
     # key = [T, H, 2D] with value = None.  The slices are strided views the kernels read in place.
     if key is None and value is None:

@@ -16,7 +16,12 @@
  *  - Every pointer in the parameter structs is a DEVICE pointer unless its name ends in `_host`.
  *  - Q is [total_q, heads, head_dim], K and V are [total_kv, heads, head_dim], row-major and
  *    contiguous; offsets are [batch + 1] exclusive prefix sums of the sequence lengths, int32 or
- *    int64 (offsets_are_int64).
+ *    int64.  The field `offsets_are_int64` of the parameter structs is a set of flags: GDPA_OFFSETS_INT64 (1) for
+ *    64-bit entries, GDPA_OFFSETS_PAIRS (2) when both offset arrays hold 2 * batch entries [start_0, end_0,
+ *    start_1, end_1, ...] instead (the reference's use_start_end_offsets,
+ *    gdpa/triton/triton_generalized_dot_product_attention.py:943-946, :4270-4274): sequences may then share or
+ *    overlap K / V rows, Q rows must not overlap.  Pairs are accepted by gdpa_build_schedule, gdpa_fwd,
+ *    gdpa_fwd_noalloc and gdpa_bwd (which then needs `dkv_accum`), not together with kv_seq_index or FP8.
  *  - The library allocates nothing and never synchronises the stream.  Scratch buffers
  *    (schedule, fp32 dQ accumulator, status word) are supplied by the caller; their sizes come
  *    from gdpa_schedule_bytes() and gdpa_bwd_workspace_bytes().
@@ -119,6 +124,9 @@ int gdpa_build_schedule(const GdpaSchedParams* params, gdpa_stream_t stream);
  * (gdpa/triton/triton_generalized_dot_product_attention.py:3099-3335) and of _flash_attn_fwd
  * (gdpa/src/interface.py:931-1254): one persistent tcgen05 kernel.
  * ------------------------------------------------------------------------------------------- */
+#define GDPA_OFFSETS_INT64 1
+#define GDPA_OFFSETS_PAIRS 2
+
 typedef struct GdpaFwdParams {
   uint32_t struct_size;       /* sizeof(GdpaFwdParams) */
   int32_t dtype;              /* GDPA_DTYPE_BF16 */
@@ -379,6 +387,11 @@ typedef struct GdpaBwdParams {
   int64_t q_strides[2];
   int64_t k_strides[2];
   int64_t v_strides[2];
+  /* With GDPA_OFFSETS_PAIRS a K / V row can belong to several sequences, so dK and dV are summed in fp32:
+   * scratch of 2 * total_kv * kv_heads * head_dim floats (dK then dV), 16-byte aligned, zeroed by gdpa_bwd, which
+   * also rounds it into dk / dv (the reference adds with atomics into zeroed gradients,
+   * gdpa/triton/triton_generalized_dot_product_attention.py:2369-2387, :3514).  Null otherwise. */
+  void* dkv_accum;
 } GdpaBwdParams;
 
 /* Bytes of the fp32 dQ accumulator for a backward over total_q rows. */

@@ -206,6 +206,32 @@ def gdpa_forward_broadcast_q(query, key, value, key_offset, activation="raw", qk
     return torch.cat(outs, dim=0)
 
 
+def gdpa_forward_start_end(query, key, value, query_pairs, key_pairs, activation="raw", qk_scale=None):
+    """The reference's ``use_start_end_offsets`` (gdpa/triton/triton_generalized_dot_product_attention.py:943-946,
+    :599-618, :4270-4274): offsets are ``[start_0, end_0, start_1, end_1, ...]``, sequence ``b`` reads Q rows
+    ``[q_pairs[2b], q_pairs[2b+1])`` and K / V rows ``[k_pairs[2b], k_pairs[2b+1])`` (which may overlap between
+    sequences) and writes the output rows of its Q range; rows no sequence owns stay zero.  Built from torch ops so
+    that autograd gives the gradients, dK / dV summed over the sequences that read a row."""
+    act = pytorch_activation(activation)
+    scale = 1.0 if qk_scale is None else float(qk_scale)
+    qp = [int(x) for x in query_pairs]
+    kp = [int(x) for x in key_pairs]
+    out = torch.zeros_like(query)
+    pieces = []
+    for b in range(len(qp) // 2):
+        qs, qe, ks, ke = qp[2 * b], qp[2 * b + 1], kp[2 * b], kp[2 * b + 1]
+        if qe <= qs:
+            continue
+        qb = query[qs:qe].transpose(0, 1)
+        kb = key[ks:ke].transpose(0, 1)
+        vb = value[ks:ke].transpose(0, 1)
+        p = act(torch.matmul(qb, kb.transpose(-1, -2))) * scale
+        pieces.append((qs, qe, torch.matmul(p, vb).transpose(0, 1)))
+    for qs, qe, ob in pieces:
+        out = torch.cat([out[:qs], ob, out[qe:]], dim=0)
+    return out
+
+
 def forward_backward_of(fn, query, key, value, grad_out):
     """(O, dQ, dK, dV) in fp32 by autograd over ``fn(q, k, v)``, for the composed variants above."""
     q = query.detach().to(torch.float32).clone().requires_grad_(True)

@@ -19,8 +19,8 @@ symlink of that name makes them resolve.  Four things are recorded:
   op body (:3461-3788), executed on the CPU by Triton's interpreter (``TRITON_INTERPRET=1``, autotuning
   off), on a jagged batch with different Q and KV lengths and ``qk_scale = 0.25``, for every activation
   of the table; plus one grouped-query case (4 query heads, 2 K/V heads), one banded case
-  (``window_size = 6``), one case with per-head activations (``ensemble_activation_list``) and one with
-  ``broadcast_q``.  These pin where the scale is applied and every gradient;
+  (``window_size = 6``), one case with per-head activations (``ensemble_activation_list``), one with
+  ``broadcast_q`` and one with ``use_start_end_offsets`` (overlapping K / V ranges).  These pin where the scale is applied and every gradient;
 * ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
 
 Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
@@ -167,6 +167,24 @@ def main(ref_root: str) -> None:
                broadcast_q=True, activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
     out.update(bcast_q=qb.numpy(), bcast_do=dob.numpy(), bcast_o=ob.numpy(), bcast_dq=resb[0].float().numpy(),
                bcast_dk=resb[1].numpy(), bcast_dv=resb[2].numpy())
+
+    # start / end offsets: [start_0, end_0, start_1, end_1, ...]; the Q ranges are disjoint (the second one leaves a
+    # gap before the third), the K / V ranges overlap, so dK / dV sum over the sequences that read a row
+    tq, tk = int(qo[-1]), int(ko[-1])
+    q_pairs = torch.tensor([0, int(qo[1]), int(qo[1]), int(qo[2]) - 1, int(qo[2]), tq], dtype=torch.int32)
+    k_pairs = torch.tensor([0, min(30, tk), min(10, tk), min(45, tk), min(20, tk), tk], dtype=torch.int32)
+    mq = int((q_pairs[1::2] - q_pairs[0::2]).max())
+    mk = int((k_pairs[1::2] - k_pairs[0::2]).max())
+    ose = fwd(q, k, v, q_pairs, k_pairs, mq, mk, qk_scale=scale, use_start_end_offsets=True, total_num_objects=tq,
+              activation="gelu_approx")
+    rese = bwd(do, q, k, v, ose, q_pairs, k_pairs, B, H, 1, mq, mk, D, D, qk_scale=scale, use_start_end_offsets=True,
+               activation_enum_int=ref_math.activation_to_int[ref_math.Activation.GeLUApprox])
+    covered = torch.zeros(tq, dtype=torch.bool)
+    for s0, e0 in zip(q_pairs[0::2].tolist(), q_pairs[1::2].tolist()):
+        covered[s0:e0] = True
+    ose[~covered] = 0  # rows no sequence owns are uninitialised memory in the reference's output (torch.empty, :3015)
+    out.update(startend_q_pairs=q_pairs.numpy(), startend_k_pairs=k_pairs.numpy(), startend_o=ose.numpy(),
+               startend_dq=rese[0].float().numpy(), startend_dk=rese[1].float().numpy(), startend_dv=rese[2].float().numpy())
 
     np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
     ids = {a.value: i for a, i in ref_math.activation_to_int.items()}

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import gdpa_oracle as orc
 from tests._util import ATOL, RTOL, assert_close, jagged_inputs, oracle_forward, oracle_forward_backward
 
 pytestmark = pytest.mark.gpu
@@ -435,3 +436,61 @@ def test_broadcast_q_one_query_sequence_for_the_batch(G, act):
     o2 = G.generalized_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), qo, ko.cuda(), LQ, max(lk), qk_scale=0.1,
                                              activation=act, broadcast_q=True)
     assert torch.equal(o2, o)
+
+
+@pytest.mark.parametrize("D,offset_dtype", [(128, torch.int64), (64, torch.int32)])
+def test_start_end_offsets_forward_backward(G, D, offset_dtype):
+    """use_start_end_offsets: per-sequence [start, end] pairs; the K / V ranges of the sequences overlap (and one
+    is shared outright), so dK / dV sum over every sequence that reads a row; one Q row belongs to no sequence."""
+    H = 2
+    q_pairs = [0, 300, 300, 429, 430, 431, 431, 700]     # row 429 is a gap; a one-row sequence
+    k_pairs = [0, 260, 100, 500, 100, 500, 450, 777]     # overlaps; sequences 1 and 2 share one K / V range
+    tq, tk = 700, 800                                    # K / V rows 777.. are read by nobody
+    g = torch.Generator().manual_seed(91)
+    q, do = (torch.randn(tq, H, D, generator=g) * 0.5).bfloat16(), (torch.randn(tq, H, D, generator=g) * 0.5).bfloat16()
+    k, v = (torch.randn(tk, H, D, generator=g) * 0.5).bfloat16(), (torch.randn(tk, H, D, generator=g) * 0.5).bfloat16()
+    qp = torch.tensor(q_pairs, dtype=offset_dtype, device="cuda")
+    kp = torch.tensor(k_pairs, dtype=offset_dtype, device="cuda")
+    mq = max(e - s for s, e in zip(q_pairs[0::2], q_pairs[1::2]))
+    mk = max(e - s for s, e in zip(k_pairs[0::2], k_pairs[1::2]))
+    scale = 1.0 / 64
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = G.generalized_dot_product_attention(qd, kd, vd, qp, kp, mq, mk, qk_scale=scale, activation="gelu_approx",
+                                            use_start_end_offsets=True, total_num_objects=tq)
+    covered = torch.ones(tq, dtype=torch.bool)
+    covered[429] = False
+    o.backward(do.cuda() * covered.view(-1, 1, 1).cuda())
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    ro, rdq, rdk, rdv = orc.forward_backward_of(
+        lambda a, b, c: orc.gdpa_forward_start_end(a, b, c, q_pairs, k_pairs, "gelu_approx", scale), q, k, v,
+        do * covered.view(-1, 1, 1))
+    assert_close(o[covered.cuda()], ro[covered], "O (start/end offsets)")
+    assert_close(qd.grad, rdq, "dQ (start/end offsets)")
+    assert_close(kd.grad, rdk, "dK (start/end offsets)")
+    assert_close(vd.grad, rdv, "dV (start/end offsets)")
+    assert float(kd.grad[777:].abs().max()) == 0.0 and float(qd.grad[429].abs().max()) == 0.0
+    # the same batch written as prefix sums where that is possible (disjoint K / V): bit-identical forward
+    qo = torch.tensor([0, 300, 700], dtype=offset_dtype, device="cuda")
+    ko = torch.tensor([0, 260, 777], dtype=offset_dtype, device="cuda")
+    a = G.generalized_dot_product_attention(qd.detach(), kd.detach(), vd.detach(), qo, ko, 400, 517, qk_scale=scale,
+                                            activation="relu")
+    b = G.generalized_dot_product_attention(qd.detach(), kd.detach(), vd.detach(),
+                                            torch.tensor([0, 300, 300, 700], dtype=offset_dtype, device="cuda"),
+                                            torch.tensor([0, 260, 260, 777], dtype=offset_dtype, device="cuda"), 400, 517,
+                                            qk_scale=scale, activation="relu", use_start_end_offsets=True, total_num_objects=tq)
+    assert torch.equal(a, b)
+
+
+def test_start_end_offsets_argument_errors(G):
+    q = torch.zeros(8, 2, 64, dtype=torch.bfloat16, device="cuda")
+    pairs = torch.tensor([0, 8], device="cuda")
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(q, q, q, pairs, pairs, 8, 8, use_start_end_offsets=True)  # total_num_objects
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(q, q, q, pairs, pairs, 8, 8, use_start_end_offsets=True, total_num_objects=8,
+                                            broadcast_q=True)
+    with pytest.raises(ValueError):
+        G.generalized_dot_product_attention(q, q, q, torch.tensor([0, 4, 8], device="cuda"),
+                                            torch.tensor([0, 4, 8], device="cuda"), 8, 8, use_start_end_offsets=True,
+                                            total_num_objects=8)  # an odd number of entries

@@ -137,6 +137,20 @@ def test_oracle_matches_reference_triton_kernels_broadcast_q(golden):
         torch.testing.assert_close(got, t(f"bcast_{name}"), atol=3e-5, rtol=3e-5)
 
 
+def test_oracle_matches_reference_triton_kernels_start_end_offsets(golden):
+    """use_start_end_offsets: [start, end] pairs per sequence, overlapping K / V ranges (dK / dV summed over the
+    sequences that read a row), a Q row that no sequence owns."""
+    t = lambda n: torch.from_numpy(golden[n])
+    scale = float(golden["triton_scale"])
+    qp, kp = golden["startend_q_pairs"], golden["startend_k_pairs"]
+    assert kp[2] < kp[1] and qp[3] < qp[4]  # the fixture really overlaps K / V and leaves a Q gap
+    res = orc.forward_backward_of(
+        lambda q, k, v: orc.gdpa_forward_start_end(q, k, v, qp, kp, "gelu_approx", scale),
+        t("triton_q"), t("triton_k"), t("triton_v"), t("triton_do"))
+    for name, got in zip(("o", "dq", "dk", "dv"), res):
+        torch.testing.assert_close(got, t(f"startend_{name}"), atol=3e-5, rtol=3e-5)
+
+
 def test_norm_pipeline_oracle_follows_the_reference_test_formulation():
     """LayerNorm(Q) -> GDPA -> + ln_q -> RMSNorm, written as the reference's megakernel test writes it
     (gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:110-127) with torch's functional norms."""
