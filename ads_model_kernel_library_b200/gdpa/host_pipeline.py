@@ -28,7 +28,7 @@ def forward_backward_host(
     qk_scale: Optional[float] = None,
     activation: str = "raw",
     out: Optional[Dict[str, torch.Tensor]] = None,
-    n_chunks: int = 8,
+    n_chunks: int = 32,
     device=None,
 ) -> Dict[str, torch.Tensor]:
     """O, dQ, dK, dV (host tensors, pinned when allocated here) of jagged GDPA for host inputs.

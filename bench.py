@@ -170,7 +170,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the number of sequences (reduced-size runs)")
     ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--e2e-chunks", type=int, default=16)
+    ap.add_argument("--e2e-chunks", type=int, default=32)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
     ap.add_argument("--norms", action="store_true",
                     help="time the forward of the GDPA-plus-norm pipeline (layer norm of Q, Q residual, RMS norm) "
