@@ -350,6 +350,8 @@ int run_mxfp8(const GdpaMxParams* p, int quantize, gdpa_stream_t stream) {
   if (p->offsets == nullptr || p->block_offsets == nullptr) return GDPA_ERR_BAD_ARG;
   if (p->total > 0 && (p->x == nullptr || p->x8 == nullptr || p->sf == nullptr)) return GDPA_ERR_BAD_ARG;
   if (p->sf_blocks < 0) return GDPA_ERR_BAD_ARG;
+  // a batch of `total` rows has at least ceil(total / 128) blocks, whatever its sequence lengths
+  if (p->sf_blocks < (p->total + kTile - 1) / kTile) return GDPA_ERR_CAPACITY;
   if (((reinterpret_cast<uintptr_t>(p->x8) | reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->sf)) & 15u) != 0)
     return GDPA_ERR_MISALIGNED;
   MxArgs a;

@@ -300,7 +300,8 @@ int gdpa_quantize_fp8_blockwise(const GdpaQuantParams* params, gdpa_stream_t str
  *     (head * ceil(head_dim / 128) + head_dim_atom) * sf_blocks + token_block.
  * sf_blocks is the number of 128-row token blocks the scale tensor is laid out for: block_offsets[batch] for
  * the reference's layout (known to a caller that has the sequence lengths on the host), or any upper bound such
- * as total / 128 + batch.  gdpa_quantize_mxfp8 is the producer the reference refers to but does not contain
+ * as total / 128 + batch (fewer than ceil(total / 128) is GDPA_ERR_CAPACITY; blocks past sf_blocks are left
+ * unprocessed).  gdpa_quantize_mxfp8 is the producer the reference refers to but does not contain
  * (quantize_varlen_mxfp8_sf_only, gdpa/src/interface.py:715-724): code = exponent field of amax * (1 / 448) in
  * fp32, plus one when its mantissa is not zero (the reference's rule for its P tile,
  * gdpa/src/activation_utils.py:444-517), element = e4m3(x * 2^(127 - code)) to nearest even, saturating; scale

@@ -82,6 +82,8 @@ def test_mxfp8_entry_points_check_arguments_before_any_cuda_call(cabi):
         assert fn(C.byref(p), None) == 1  # null data with total > 0
         p.x, p.x8, p.sf, p.sf_blocks = 16, 32, 52, 1
         assert fn(C.byref(p), None) == 5  # GDPA_ERR_MISALIGNED: scale tensor not 16-byte aligned
+        p.sf, p.total, p.sf_blocks = 64, 300, 2
+        assert fn(C.byref(p), None) == 8  # GDPA_ERR_CAPACITY: 300 rows need at least three blocks of scales
 
 
 def test_schedule_and_workspace_sizes(cabi):
