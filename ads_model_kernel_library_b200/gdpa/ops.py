@@ -305,18 +305,21 @@ def _gdpa_forward_softmax_op(
     max_seq_len_kv: int,
     qk_scale: float,
     window_size: int = -1,
+    start_end_offsets: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Softmax forward that also returns the base-2 log-sum-exp ``[H, total_q]`` its backward needs."""
-    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16)
+    batch, H, D = _check_inputs(query, key, value, query_offset, key_offset, torch.bfloat16, start_end=start_end_offsets)
     with torch.cuda.device(query.device):
         o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         lse = torch.zeros((H, query.shape[0]), dtype=torch.float32, device=query.device)
         if query.shape[0] == 0 or batch == 0:
             return o, lse
-        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H, query.shape[0],
-                                max_seq_len_q, max_seq_len_kv)
+        sched = _build_schedule(_cabi.GDPA_SCHED_FWD, query_offset, key_offset, batch, H,
+                                batch * max_seq_len_q if start_end_offsets else query.shape[0],
+                                max_seq_len_q, max_seq_len_kv, start_end=start_end_offsets)
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, SOFTMAX_ID, sched, _cabi.GDPA_DTYPE_BF16)
+        p.offsets_are_int64 = _offset_flags(query_offset, start_end_offsets)
         p.lse = lse.data_ptr()
         p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
@@ -325,24 +328,25 @@ def _gdpa_forward_softmax_op(
 
 
 @_gdpa_forward_softmax_op.register_fake
-def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, window_size=-1):
+def _(query, key, value, query_offset, key_offset, max_seq_len_q, max_seq_len_kv, qk_scale, window_size=-1,
+      start_end_offsets=False):
     return query.new_empty(query.shape), torch.empty((query.shape[1], query.shape[0]), dtype=torch.float32, device=query.device)
 
 
 def _softmax_setup_context(ctx, inputs, output):
-    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, window_size = inputs
+    query, key, value, query_offset, key_offset, max_q, max_kv, qk_scale, window_size, start_end = inputs
     o, lse = output
     ctx.save_for_backward(query, key, value, query_offset, key_offset, o, lse)
-    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.window_size = max_q, max_kv, qk_scale, window_size
+    ctx.max_q, ctx.max_kv, ctx.qk_scale, ctx.window_size, ctx.start_end = max_q, max_kv, qk_scale, window_size, start_end
 
 
 def _softmax_backward(ctx, do, dlse):
     query, key, value, query_offset, key_offset, o, lse = ctx.saved_tensors
     dq, dk, dv = torch.ops.gdpa.generalized_dot_product_attention_backward(
         do, query, key, value, query_offset, key_offset, ctx.max_q, ctx.max_kv, ctx.qk_scale, SOFTMAX_ID, o, lse,
-        ctx.window_size
+        ctx.window_size, ctx.start_end
     )
-    return dq, dk, dv, None, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None, None
 
 
 _gdpa_forward_softmax_op.register_autograd(_softmax_backward, setup_context=_softmax_setup_context)
@@ -500,7 +504,7 @@ def generalized_dot_product_attention(
     activation id per head) are composed on the host from calls of the same kernels;
     ``use_start_end_offsets`` (offsets ``[start_0, end_0, start_1, end_1, ...]``: sequences may share or overlap
     K / V rows; dK and dV are then summed in fp32 over the sequences that read a row) is supported forward and
-    backward for the element-wise activations.  Every other
+    backward.  Every other
     non-default option raises, as the reference does for masks and causality (:3138-3139).
     """
     if attn_mask is not None:
@@ -536,11 +540,13 @@ def generalized_dot_product_attention(
         if ad_to_request_offset is not None or ensemble_activation_list or output_offset is not None:
             raise NotImplementedError("start/end offsets together with ad_to_request_offset, ensemble_activation_list or "
                                       "output_offset are not supported")
-        if act_id == SOFTMAX_ID:
-            raise NotImplementedError("start/end offsets are not supported for the softmax variant")
         window = -1 if window_size is None else int(window_size)
         if window_size is not None and window < 0:
             raise ValueError("window_size must be non-negative")
+        if act_id == SOFTMAX_ID:
+            return torch.ops.gdpa.generalized_dot_product_attention_softmax(
+                expect_contiguous(query), key, value, query_offset.contiguous(), key_offset.contiguous(), int(max_seq_len_q),
+                int(max_seq_len_kv), scale, window, True)[0]
         return torch.ops.gdpa.generalized_dot_product_attention(
             expect_contiguous(query), key, value, query_offset.contiguous(), key_offset.contiguous(), int(max_seq_len_q),
             int(max_seq_len_kv), scale, act_id, window, True)

@@ -212,7 +212,7 @@ def gdpa_forward_start_end(query, key, value, query_pairs, key_pairs, activation
     ``[q_pairs[2b], q_pairs[2b+1])`` and K / V rows ``[k_pairs[2b], k_pairs[2b+1])`` (which may overlap between
     sequences) and writes the output rows of its Q range; rows no sequence owns stay zero.  Built from torch ops so
     that autograd gives the gradients, dK / dV summed over the sequences that read a row."""
-    act = pytorch_activation(activation)
+    act = None if activation == "softmax" else pytorch_activation(activation)
     scale = 1.0 if qk_scale is None else float(qk_scale)
     qp = [int(x) for x in query_pairs]
     kp = [int(x) for x in key_pairs]
@@ -225,7 +225,8 @@ def gdpa_forward_start_end(query, key, value, query_pairs, key_pairs, activation
         qb = query[qs:qe].transpose(0, 1)
         kb = key[ks:ke].transpose(0, 1)
         vb = value[ks:ke].transpose(0, 1)
-        p = act(torch.matmul(qb, kb.transpose(-1, -2))) * scale
+        sc = torch.matmul(qb, kb.transpose(-1, -2))
+        p = F.softmax(sc * scale, dim=-1) if act is None else act(sc) * scale
         pieces.append((qs, qe, torch.matmul(p, vb).transpose(0, 1)))
     for qs, qe, ob in pieces:
         out = torch.cat([out[:qs], ob, out[qe:]], dim=0)

@@ -438,8 +438,9 @@ def test_broadcast_q_one_query_sequence_for_the_batch(G, act):
     assert torch.equal(o2, o)
 
 
-@pytest.mark.parametrize("D,offset_dtype", [(128, torch.int64), (64, torch.int32)])
-def test_start_end_offsets_forward_backward(G, D, offset_dtype):
+@pytest.mark.parametrize("D,offset_dtype,act", [(128, torch.int64, "gelu_approx"), (64, torch.int32, "gelu_approx"),
+                                                 (128, torch.int32, "softmax")])
+def test_start_end_offsets_forward_backward(G, D, offset_dtype, act):
     """use_start_end_offsets: per-sequence [start, end] pairs; the K / V ranges of the sequences overlap (and one
     is shared outright), so dK / dV sum over every sequence that reads a row; one Q row belongs to no sequence."""
     H = 2
@@ -453,9 +454,9 @@ def test_start_end_offsets_forward_backward(G, D, offset_dtype):
     kp = torch.tensor(k_pairs, dtype=offset_dtype, device="cuda")
     mq = max(e - s for s, e in zip(q_pairs[0::2], q_pairs[1::2]))
     mk = max(e - s for s, e in zip(k_pairs[0::2], k_pairs[1::2]))
-    scale = 1.0 / 64
+    scale = 0.5 if act == "softmax" else 1.0 / 64
     qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
-    o = G.generalized_dot_product_attention(qd, kd, vd, qp, kp, mq, mk, qk_scale=scale, activation="gelu_approx",
+    o = G.generalized_dot_product_attention(qd, kd, vd, qp, kp, mq, mk, qk_scale=scale, activation=act,
                                             use_start_end_offsets=True, total_num_objects=tq)
     covered = torch.ones(tq, dtype=torch.bool)
     covered[429] = False
@@ -463,7 +464,7 @@ def test_start_end_offsets_forward_backward(G, D, offset_dtype):
     torch.cuda.synchronize()
     assert G.kernel_status() == 0
     ro, rdq, rdk, rdv = orc.forward_backward_of(
-        lambda a, b, c: orc.gdpa_forward_start_end(a, b, c, q_pairs, k_pairs, "gelu_approx", scale), q, k, v,
+        lambda a, b, c: orc.gdpa_forward_start_end(a, b, c, q_pairs, k_pairs, act, scale), q, k, v,
         do * covered.view(-1, 1, 1))
     assert_close(o[covered.cuda()], ro[covered], "O (start/end offsets)")
     assert_close(qd.grad, rdq, "dQ (start/end offsets)")
