@@ -364,6 +364,7 @@ def _gdpa_forward_shared_kv_op(
     max_seq_len_kv: int,
     qk_scale: float,
     activation: int,
+    window_size: int = -1,
 ) -> torch.Tensor:
     """Forward where Q sequence i attends to KV sequence ``kv_seq_index[i]`` (the reference's
     ``ad_to_request_offset`` inference path, where many ads share the KV of one request)."""
@@ -380,13 +381,15 @@ def _gdpa_forward_shared_kv_op(
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
         p.kv_seq_index = kv_index.data_ptr()
+        p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
     return o
 
 
 @_gdpa_forward_shared_kv_op.register_fake
-def _(query, key, value, query_offset, key_offset, kv_seq_index, max_seq_len_q, max_seq_len_kv, qk_scale, activation):
+def _(query, key, value, query_offset, key_offset, kv_seq_index, max_seq_len_q, max_seq_len_kv, qk_scale, activation,
+      window_size=-1):
     return query.new_empty(query.shape)
 
 
@@ -584,11 +587,9 @@ def generalized_dot_product_attention(
         return _ensemble(query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale,
                          act_id, window, [int(a) for a in ensemble_activation_list])
     if ad_to_request_offset is not None:
-        if window >= 0:
-            raise NotImplementedError("window_size together with ad_to_request_offset is not supported")
         return torch.ops.gdpa.generalized_dot_product_attention_shared_kv(
             query, key, value, query_offset, key_offset, ad_to_request_offset, int(max_seq_len_q), int(max_seq_len_kv),
-            scale, act_id
+            scale, act_id, window
         )
     return _dispatch(query, key, value, query_offset, key_offset, int(max_seq_len_q), int(max_seq_len_kv), scale, act_id,
                      window)

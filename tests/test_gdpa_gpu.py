@@ -304,6 +304,13 @@ def test_shared_kv_sequences_via_ad_to_request_offset(G):
     ko_exp = torch.tensor(np.concatenate([[0], np.cumsum([lk[r] for r in ad2req])]))
     ref = orc.gdpa_forward(q.float(), k_exp.float(), v_exp.float(), qo, ko_exp, "gelu_approx", 0.1)
     assert_close(o, ref, "O[shared KV]")
+    # the same with a band |q - kv| <= 20 of sequence-local positions
+    ow = G.generalized_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), qo.cuda(), ko.cuda(), max(lq), max(lk),
+                                             ad_to_request_offset=torch.tensor(ad2req).cuda(), qk_scale=0.1,
+                                             activation="gelu_approx", window_size=20)
+    torch.cuda.synchronize()
+    refw = orc.gdpa_forward(q.float(), k_exp.float(), v_exp.float(), qo, ko_exp, "gelu_approx", 0.1, window_size=20)
+    assert_close(ow, refw, "O[shared KV, banded]")
     qg = q.cuda().requires_grad_(True)
     og = G.generalized_dot_product_attention(qg, k.cuda(), v.cuda(), qo.cuda(), ko.cuda(), max(lq), max(lk),
                                              ad_to_request_offset=torch.tensor(ad2req).cuda(), activation="relu")
