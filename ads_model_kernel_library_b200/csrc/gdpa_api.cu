@@ -105,7 +105,7 @@ int check_common(const P* p) {
   if (p->max_seq_len_q < 0 || p->max_seq_len_kv < 0) return GDPA_ERR_BAD_ARG;
   if (p->window_plus_one < 0 || p->window_plus_one > (1 << 29)) return GDPA_ERR_BAD_ARG;
   if (p->head_dim != 64 && p->head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM;
-  if (p->q_offsets == nullptr || p->kv_offsets == nullptr || p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
+  if (p->q_offsets == nullptr || p->kv_offsets == nullptr) return GDPA_ERR_BAD_ARG;
   if ((p->offsets_are_int64 & ~(GDPA_OFFSETS_INT64 | GDPA_OFFSETS_PAIRS)) != 0) return GDPA_ERR_BAD_ARG;
   // TMA coordinates are 32-bit row indices.
   if (p->total_q >= (1ll << 31) || p->total_kv >= (1ll << 31)) return GDPA_ERR_BAD_ARG;
@@ -183,21 +183,32 @@ int gdpa_build_schedule(const GdpaSchedParams* p, gdpa_stream_t stream) {
   a.sched = static_cast<int*>(p->schedule);
   a.capacity_items = (p->schedule_bytes - kSchedHeaderInts * 4) / 16;
   a.kv_index = p->kv_seq_index;
+  if (p->kv_batch < 0) return GDPA_ERR_BAD_ARG;
+  a.kv_batch = (p->kv_seq_index != nullptr && p->kv_batch > 0) ? p->kv_batch : p->batch;
   int rc = launch_build_schedule(a, static_cast<cudaStream_t>(stream));
   if (rc == 0) g_launches.fetch_add(1);
   return rc;
 }
 
-static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
+}  // extern "C"
+#pragma GCC visibility pop
+
+// Everything gdpa_fwd / gdpa_fwd_fp8 check on the host before they touch the device, in one place so that
+// gdpa_fwd_noalloc can run the same checks before it writes its shared schedule array.
+int gdpa::fwd_check_params(const GdpaFwdParams* p, bool fp8, bool needs_schedule) {
   int rc = check_common(p);
   if (rc != GDPA_OK) return rc;
+  if (needs_schedule && p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
   if (p->dtype != (fp8 ? GDPA_DTYPE_FP8_E4M3 : GDPA_DTYPE_BF16)) return GDPA_ERR_UNSUPPORTED_DTYPE;
   const int act = act_class_from_id(p->activation);
   if (act < 0) return GDPA_ERR_UNSUPPORTED_ACT;
+  if (p->kv_batch < 0) return GDPA_ERR_BAD_ARG;
   if (p->total_q == 0 || p->batch == 0) return GDPA_OK;
   if (p->q == nullptr || p->o == nullptr) return GDPA_ERR_BAD_ARG;
   if (p->total_kv > 0 && (p->k == nullptr || p->v == nullptr)) return GDPA_ERR_BAD_ARG;
-  if ((reinterpret_cast<uintptr_t>(p->o) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  if (((reinterpret_cast<uintptr_t>(p->o) | reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k) |
+        reinterpret_cast<uintptr_t>(p->v)) & 15u) != 0)
+    return GDPA_ERR_MISALIGNED;
   if (fp8 && (p->q_scales == nullptr || p->k_scales == nullptr || p->v_scales == nullptr ||
               p->q_block_offsets == nullptr || p->kv_block_offsets == nullptr))
     return GDPA_ERR_BAD_ARG;
@@ -206,6 +217,18 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   if ((p->residual != nullptr || p->row_sumsq != nullptr) && (fp8 || act == ACT_SOFTMAX)) return GDPA_ERR_BAD_ARG;
   if ((p->offsets_are_int64 & GDPA_OFFSETS_PAIRS) != 0 && (fp8 || p->kv_seq_index != nullptr)) return GDPA_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(p->residual) & 15u) != 0) return GDPA_ERR_MISALIGNED;
+  return GDPA_OK;
+}
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
+  int rc = fwd_check_params(p, fp8, true);
+  if (rc != GDPA_OK) return rc;
+  if (p->total_q == 0 || p->batch == 0) return GDPA_OK;
+  const int act = act_class_from_id(p->activation);
+  const int kv_heads = p->kv_heads > 0 ? p->kv_heads : p->heads;
   DeviceInfo di;
   rc = device_info(&di);
   if (rc != GDPA_OK) return rc;
@@ -249,6 +272,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   l.args.window = p->window_plus_one > 0 ? p->window_plus_one - 1 : -1;
   l.args.residual = static_cast<const __nv_bfloat16*>(p->residual);
   l.args.row_sumsq = p->row_sumsq;
+  l.args.total_kv = p->total_kv;
+  l.args.kv_batch = (p->kv_seq_index != nullptr && p->kv_batch > 0) ? p->kv_batch : p->batch;
   l.args.q_scales = p->q_scales;
   l.args.k_scales = p->k_scales;
   l.args.v_scales = p->v_scales;
@@ -410,6 +435,7 @@ int gdpa_norm_rows_bwd(const GdpaNormBwdParams* p, gdpa_stream_t stream) {
 int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   int rc = check_common(p);
   if (rc != GDPA_OK) return rc;
+  if (p->schedule == nullptr) return GDPA_ERR_BAD_ARG;
   if (p->dtype != GDPA_DTYPE_BF16) return GDPA_ERR_UNSUPPORTED_DTYPE;
   const int act = act_class_from_id(p->activation);
   if (act < 0) return GDPA_ERR_UNSUPPORTED_ACT;
@@ -481,6 +507,7 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.args.total_q = p->total_q;
   l.args.dk_acc = pairs ? static_cast<float*>(p->dkv_accum) : nullptr;
   l.args.dv_acc = pairs ? static_cast<float*>(p->dkv_accum) + elems_kv : nullptr;
+  l.args.total_kv = p->total_kv;
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;

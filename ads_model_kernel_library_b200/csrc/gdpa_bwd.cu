@@ -19,8 +19,9 @@
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
 // dQ tiles are drained by a dedicated warpgroup (whole tile into registers, TMEM released, then each
 // warp stages its 32 rows in shared memory) and added into an fp32 accumulator by TMA reduce-add; a
-// second kernel rounds the accumulator to bf16.  Q rows of a tile beyond the sequence carry dS = 0, so what the reduce adds to
-// the rows of the next sequence is exactly zero; rows beyond the tensor are clipped by the TMA unit.
+// second kernel rounds the accumulator to bf16.  Q rows of a tile beyond the sequence are forced to zero before they are
+// staged, so what the reduce adds to the rows of the next sequence is exactly zero; rows beyond the tensor are clipped by
+// the TMA unit.
 //
 // Softmax: P^T = 2^(c S^T - lse[q]) from the forward's log-sum-exp and dS = scale P (dP - dPsum[q]); the
 // per-column statistics of a Q tile reach the element-wise warps through shared memory.
@@ -31,8 +32,16 @@
 // ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
 // Masking is by zero: score entries whose KV row or Q column lies beyond the sequence are zeroed
-// both in act(S) and in act'(S) (act'(0) is not 0 for GELU / SiLU), so rows of other sequences that
-// a tile overlaps contribute exactly zero.
+// both in act(S) and in act'(S) (act'(0) is not 0 for GELU / SiLU), and dP there is replaced by zero before
+// it is multiplied, so rows of other sequences that a tile overlaps contribute exactly zero whatever they
+// hold (the reference's per-sequence block loads read them as zero,
+// gdpa/triton/triton_generalized_dot_product_attention.py:1575-1600).  The contractions always cover whole tiles, so
+// on a ragged tile the rows of Q, dO (last Q tile of a sequence) and K (last KV tile) beyond the sequence are
+// zero-filled in shared memory by the element-wise warps before they hand the tile's P^T to the MMA thread, i.e.
+// before dV, dK and dQ read those rows as the contraction dimension (0 x Inf would not be zero); S^T and dP^T, which
+// read them earlier, only get columns / rows from them that the selects above discard.
+#include <type_traits>
+
 #include "gdpa_common.cuh"
 #include "gdpa_launch.h"
 
@@ -71,6 +80,7 @@ enum BwdBar : int {
   BB_COUNT = 19
 };
 
+
 template <int D>
 struct BwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;
@@ -91,26 +101,12 @@ struct BwdSmem {
   static constexpr int kDynBytes = kBytes + 1024;
 };
 
-// How dQ tiles leave the SM: staged in shared memory and added by TMA reduce (full 128-byte lines at
-// L2, but 128 KB of shared-memory traffic per tile), or straight from registers with vector reductions.
-// Three alternatives were measured on the B=512 uniform workload and dropped.  (0) Sixteen element-wise warps
-// (four column quarters) instead of eight: the phases did not get shorter (2 000 and 770 cycles per Q tile
-// against 2 180 and 740: they are bound by FMA-pipe and issue throughput of the four SM sub-partitions, not by
-// latency), and the dQ drain, left with 80 registers, released TMEM later: 5 830 instead of 4 570 cycles per
-// Q tile.  (setmaxnreg only moves registers inside the CTA's own allocation: increases that ask for more than
-// the decreases free wait forever.)  (1) Adding dQ tiles to the
-// accumulator straight from registers with red.global.add.v4.f32 (no shared-memory staging): 578 instead
-// of 803 TFLOP/s, the 16-byte reductions to 32 different 128-byte lines per instruction saturate the
-// LSU / L2 path.  (2) Reading the A operand of dK from shared memory and issuing dQ before dK (the drain
-// of dQ then overlaps dK, at 32 KB more shared-memory traffic per Q tile): 4 957 instead of 4 815 cycles
-// per Q tile.
-//
-// The thread that issues the MMAs is on the critical path of every Q tile: whatever it executes between two
-// waits delays the tensor pipe.  Keeping the parities of its two Q stages in one register (bit st) instead of
-// an array indexed by st (which lived in local memory) took 8 - 10 % off the kernel, compiling its cycle
-// stamps out 6 %, building the operand descriptors once per role 1 %.  Two changes elsewhere measured no gain
-// and were dropped: one barrier arrival per warp instead of one per thread (35.7 - 36.3 against 35.3 - 35.8 ms),
-// and an L2 prefetch by the loader of the next work item's K / V tiles (35.6 - 36.8 against 35.0 - 35.4 ms).
+// How dQ tiles leave the SM: staged in shared memory (per-warp 32 x 32 fp32 slabs) and added into the fp32
+// accumulator by TMA reduce, which writes full 128-byte lines at L2; vector reductions straight from registers
+// saturate the LSU / L2 atomic path.  The thread that issues the MMAs is on the critical path of every Q tile:
+// whatever it executes between two waits delays the tensor pipe, so its per-tile state lives in registers (stage
+// parities as bits of one word, operand descriptors built once per role) and full tiles take a path with no test
+// per MMA.
 
 #define GDPA_WAIT(bar_idx, parity, role)                                                                   \
   if (!mbar_wait(bar_base + 8u * (bar_idx), (parity), abort_flag, a.status, ((bar_idx) << 8) | (role))) \
@@ -167,6 +163,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
   const int n_items = a.sched[0];
+  const SeqLimits lim = {a.total_q, a.total_kv, 0};
 
   constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
   // S^T / dP^T: A and B both K-major (head dim contiguous), M = N = 128.
@@ -185,7 +182,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         WorkWalker walker(n_items);
         int idx;
         while (walker.next(idx)) {
-          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
           int m0, nq1;  // first Q tile and number of Q tiles of one query head this item visits
           bwd_q_range(w, a.window, m0, nq1);
           const int nq = nq1 * a.kv_group;  // ... over every query head of this K / V head's group
@@ -255,7 +252,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         WorkWalker walker(n_items);
         int idx;
         while (walker.next(idx)) {
-          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+          const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
           int m0, nq1;
           bwd_q_range(w, a.window, m0, nq1);
           const int nq = nq1 * a.kv_group;
@@ -342,6 +339,13 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float scale = a.scale, hscale = 0.5f * a.scale;
     uint8_t* sds_row = smem + L::kDsOff + half * L::kHalfBytes + row * 128;
     uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0, st_phase = 0;
+    // rows [lo, hi) of every 128-byte-row box of a tile, by the 256 element-wise threads
+    auto zero_rows = [&](uint8_t* tile, int lo, int hi) {
+#pragma unroll
+      for (int hf = 0; hf < D / 64; ++hf)
+        for (int off = lo * 128 + (threadIdx.x - 128) * 16; off < hi * 128; off += 256 * 16)
+          *reinterpret_cast<uint4*>(tile + hf * L::kHalfBytes + off) = make_uint4(0, 0, 0, 0);
+    };
     int tr = 0;
     const bool tracer = (threadIdx.x == 128);
     constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
@@ -352,7 +356,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
       int m0, nq1;
       bwd_q_range(w, a.window, m0, nq1);
       const int nq = nq1 * a.kv_group;
@@ -466,6 +470,21 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st16(tS + half * 64 + c * 16, pk);
         }
         tmem_wait_st();
+        // (a test on the tile's geometry alone, the same for all 256 threads: with a band `full` differs between warps)
+        if ((a.window < 0) ? !full : ((w.blk + 1) * kTile > w.lkv || w.lq - mm * kTile < kTile)) {
+          // A ragged tile (rare: the last Q tile of a sequence, or every tile of its last KV tile).  The rows of Q, dO
+          // and K beyond the sequence belong to the next one; dV, dK and dQ contract over them against zeros, and
+          // 0 x Inf is not zero: clear them before the MMA thread is allowed to go on.  dp_phase has not been flipped
+          // for this tile yet, so it is the parity of the dO barrier and the stage of the Q tile (all flip per tile).
+          const int q_valid = w.lq - mm * kTile;
+          if (q_valid < kTile) {
+            GDPA_WAIT_WARP(BB_DO_FULL, dp_phase, ST_ROLE_ACT);  // the dO tile has landed
+            zero_rows(smem + L::kDoOff, q_valid, kTile);
+            zero_rows(smem + L::kQOff + dp_phase * L::kTileBytes, q_valid, kTile);
+          }
+          if (m == 0 && w.lkv - w.blk * kTile < kTile) zero_rows(smem + L::kKOff, w.lkv - w.blk * kTile, kTile);
+          fence_proxy_async_smem();
+        }
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_P_FULL);
         if (tracer) GDPA_TRACE(a, tr * 32 + 10);
@@ -474,43 +493,65 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         dp_phase ^= 1u;
         tc_fence_after();
         if (tracer) GDPA_TRACE(a, tr * 32 + 11);
-        tmem_ld32(tDP + half * 64, ra);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t(&cur)[32] = c ? rb : ra;
-          tmem_wait_ld();
-          tmem_regs_ready(cur);
-          if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t d[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float d0, d1;
-              if constexpr (kSoftmax) {
-                const float2 ps = *reinterpret_cast<const float2*>(stat_dps + (m & 1) * kTile + half * 64 + c * 32 + 8 * j + 2 * e);
-                float p0, p1;
-                unpack_f32x2(g2[c * 16 + 4 * j + e], p0, p1);
-                d0 = p0 * (__uint_as_float(cur[8 * j + 2 * e]) - ps.x) * scale;
-                d1 = p1 * (__uint_as_float(cur[8 * j + 2 * e + 1]) - ps.y) * scale;
-              } else {
-                unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e],
-                                       pack_f32x2(__uint_as_float(cur[8 * j + 2 * e]), __uint_as_float(cur[8 * j + 2 * e + 1]))),
-                             d0, d1);
-              }
-              d[e] = pack_bf16x2(d0, d1);
+        // dS^T = act'(S^T) * dP^T for this thread's 64 columns.  Two instantiations, chosen per tile: the common one has
+        // no test per element; on a ragged tile dP outside the sequence (rows and columns that come from other
+        // sequences' tokens) is replaced by zero, so that the product with act' = 0 is zero whatever it held.  (A
+        // separate instantiation rather than a fix-up of the loaded registers inside a branch: merging such a branch
+        // back costs a register move per value on the common path.)
+        auto ds_phase = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
+          int lo = 0, hi = kTile;
+          if constexpr (kMasked) {
+            hi = row_valid ? min(kTile, w.lq - mm * kTile) : 0;
+            if (a.window >= 0) {
+              lo = max(lo, kv_local - a.window - mm * kTile);
+              hi = min(hi, kv_local + a.window - mm * kTile + 1);
             }
-            // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
-            *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
-            pk[4 * j + 0] = d[0];
-            pk[4 * j + 1] = d[1];
-            pk[4 * j + 2] = d[2];
-            pk[4 * j + 3] = d[3];
           }
-          // the same values as the A operand of dK, over dP^T columns this half has already read
-          tmem_st16(tDP + half * 64 + c * 16, pk);
-        }
+          tmem_ld32(tDP + half * 64, ra);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t(&cur)[32] = c ? rb : ra;
+            tmem_wait_ld();
+            tmem_regs_ready(cur);
+            if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t d[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(cur[8 * j + 2 * e]), x1 = __uint_as_float(cur[8 * j + 2 * e + 1]);
+                if constexpr (kMasked) {
+                  const int col = half * 64 + c * 32 + 8 * j + 2 * e;
+                  x0 = (col >= lo && col < hi) ? x0 : 0.f;
+                  x1 = (col + 1 >= lo && col + 1 < hi) ? x1 : 0.f;
+                }
+                float d0, d1;
+                if constexpr (kSoftmax) {
+                  const float2 ps = *reinterpret_cast<const float2*>(stat_dps + (m & 1) * kTile + half * 64 + c * 32 + 8 * j + 2 * e);
+                  float p0, p1;
+                  unpack_f32x2(g2[c * 16 + 4 * j + e], p0, p1);
+                  d0 = p0 * (x0 - ps.x) * scale;
+                  d1 = p1 * (x1 - ps.y) * scale;
+                } else {
+                  unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e], pack_f32x2(x0, x1)), d0, d1);
+                }
+                d[e] = pack_bf16x2(d0, d1);
+              }
+              // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
+              *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
+              pk[4 * j + 0] = d[0];
+              pk[4 * j + 1] = d[1];
+              pk[4 * j + 2] = d[2];
+              pk[4 * j + 3] = d[3];
+            }
+            // the same values as the A operand of dK, over dP^T columns this half has already read
+            tmem_st16(tDP + half * 64 + c * 16, pk);
+          }
+        };
+        if (full) ds_phase(std::false_type{});
+        else ds_phase(std::true_type{});
         tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before();
@@ -570,7 +611,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     WorkWalker walker(n_items);
     int idx;
     while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv);
+      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
       int m0, nq1;
       bwd_q_range(w, a.window, m0, nq1);
       const int nq = nq1 * a.kv_group;
@@ -596,24 +637,37 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 15);
+        // Two instantiations of the staging loop, chosen per tile.  Rows of a ragged tile beyond the sequence belong to
+        // the next one: their dS is zero, but a zero times a non-finite K row of THIS sequence is not, so what would be
+        // added to those rows is forced to zero (rare path; a fix-up of the registers inside a branch would cost a move
+        // per value on the common path).
+        auto stage_and_reduce = [&](auto masked_tag) {
+          constexpr bool kMasked = decltype(masked_tag)::value;
+          uint32_t keep = 0xffffffffu;
+          if constexpr (kMasked) keep = (mm * kTile + warp * 32 + lane < w.lq) ? 0xffffffffu : 0u;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          const uint32_t buf = slab & 1u;
-          // the reduce that read this staging buffer two slabs ago must have finished reading it
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
+          for (int c = 0; c < D / 32; ++c) {
+            const uint32_t buf = slab & 1u;
+            // the reduce that read this staging buffer two slabs ago must have finished reading it
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
-                make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
-            tma_store_commit();
+            for (int j = 0; j < 8; ++j) {
+              uint4 v = make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
+              if constexpr (kMasked) v = make_uint4(v.x & keep, v.y & keep, v.z & keep, v.w & keep);
+              *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
+              tma_store_commit();
+            }
+            ++slab;
           }
-          ++slab;
-        }
+        };
+        if (mm * kTile + warp * 32 + 32 > w.lq) stage_and_reduce(std::true_type{});
+        else stage_and_reduce(std::false_type{});
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 16);
         ++tr;
       }

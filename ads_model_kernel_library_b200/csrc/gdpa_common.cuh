@@ -53,10 +53,9 @@ __device__ __forceinline__ void seq_bounds(const void* p, int b, int flags, long
 }
 
 // Cycle stamps for performance analysis: CTA 0 writes clock64() into slot `slot` of the trace buffer
-// when one was registered with gdpa_debug_set_trace(); otherwise a single predicated-off store.  Compiled in
-// where GDPA_ENABLE_TRACE is defined before this header is included: the forward kernel keeps its stamps (without
-// them it measured 3 % slower, an effect of instruction placement), the backward kernel has them only in builds
-// with -DGDPA_ENABLE_TRACE (its MMA-issuing thread is 6 % faster without the eight tests per Q tile).
+// when one was registered with gdpa_debug_set_trace().  Compiled in only in builds with -DGDPA_ENABLE_TRACE
+// (the pointer tests sit in the MMA-issuing threads, which are on the critical path of every tile); the
+// default build has none.
 constexpr int kTraceSlots = 16384;
 #ifdef GDPA_ENABLE_TRACE
 #define GDPA_TRACE(args, slot)                                                                  \
@@ -71,30 +70,49 @@ constexpr int kTraceSlots = 16384;
 // One work item of a schedule, with the sequence geometry it refers to.
 struct Work {
   int b, h, blk;
+  int kb;  // entry of the KV offsets the sequence reads (b unless a kv_index is given)
   long long q_start, kv_start;
   int lq, lkv;
 };
+
+// What the offsets may address: rows of the Q-side and KV-side tensors and entries of the KV offsets.  Sequence
+// bounds read from the offset arrays are clamped to these, so that a malformed offset array (an entry beyond the
+// tensor, a decreasing pair, a kv_index entry beyond the KV batch) cannot make a kernel store outside a tensor; the
+// result for such a sequence is unspecified but in bounds.  Validation proper is the host's job.
+struct SeqLimits {
+  long long total_q, total_kv;
+  int kv_batch;  // sequences the KV offsets describe
+};
+
+__device__ __forceinline__ long long clamp_ll(long long x, long long lo, long long hi) { return x < lo ? lo : (x > hi ? hi : x); }
 
 // `kv_index` (optional, same integer type as the offsets) maps a sequence to the entry of the KV offsets
 // it reads: the reference's ad_to_request_offset, where many Q sequences share one KV sequence
 // (gdpa/triton/triton_generalized_dot_product_attention.py:3961-3966).
 __device__ __forceinline__ Work load_work(const int* sched, int idx, const void* q_off, const void* kv_off, int is64,
-                                          int max_q, int max_kv, const void* kv_index = nullptr) {
+                                          int max_q, int max_kv, const SeqLimits& lim, const void* kv_index = nullptr) {
   const int4 it = reinterpret_cast<const int4*>(sched + kSchedHeaderInts)[idx];
   Work w;
   w.b = it.x;
   w.h = it.y;
   w.blk = it.z;
-  const int kb = kv_index != nullptr ? static_cast<int>(load_offset(kv_index, w.b, is64)) : w.b;
+  int kb = w.b;
+  if (kv_index != nullptr) {
+    kb = static_cast<int>(load_offset(kv_index, w.b, is64));
+    kb = kb < 0 ? 0 : (kb >= lim.kv_batch ? lim.kv_batch - 1 : kb);
+  }
   long long q_end, kv_end;
   seq_bounds(q_off, w.b, is64, w.q_start, q_end);
   seq_bounds(kv_off, kb, is64, w.kv_start, kv_end);
-  long long lq = q_end - w.q_start;
-  long long lkv = kv_end - w.kv_start;
+  w.kb = kb;
+  w.q_start = clamp_ll(w.q_start, 0, lim.total_q);
+  w.kv_start = clamp_ll(w.kv_start, 0, lim.total_kv);
+  q_end = clamp_ll(q_end, w.q_start, lim.total_q);
+  kv_end = clamp_ll(kv_end, w.kv_start, lim.total_kv);
+  const long long lq = q_end - w.q_start;
+  const long long lkv = kv_end - w.kv_start;
   w.lq = static_cast<int>(lq < max_q ? lq : max_q);
   w.lkv = static_cast<int>(lkv < max_kv ? lkv : max_kv);
-  if (w.lq < 0) w.lq = 0;
-  if (w.lkv < 0) w.lkv = 0;
   return w;
 }
 
@@ -181,11 +199,8 @@ __device__ __forceinline__ float act_scaled(float x, float scale, float hscale) 
 }
 
 // Two activations at once, packed bf16x2 result (x0 in the low half).  GELU-tanh and SiLU use packed
-// f32x2 arithmetic around the two MUFU evaluations; the other classes fall back to the scalar form.
-// Measured on B200: tanh.approx.f32 and ex2.approx both issue at 8 cycles per warp instruction and SM
-// sub-partition, the two-value tanh.approx.f16x2 at 16 (no faster per element), fma.rn.f32x2 at 2 (it saves
-// issue slots, not FMA-pipe cycles), and sigmoid built from ex2 plus a Newton reciprocal costs more issue
-// slots than it saves; the plain f32 tanh below was the fastest of the three.
+// f32x2 arithmetic around the two MUFU evaluations (fewer issue slots; tanh.approx.f32 is the cheapest
+// tanh per element on this part); the other classes fall back to the scalar form.
 template <int ACT>
 __device__ __forceinline__ uint32_t act_scaled_pair_bf16(float x0, float x1, float scale, float hscale) {
   if constexpr (ACT == ACT_GELU_TANH) {

@@ -42,6 +42,8 @@ struct FwdArgs {
   // [total_q] fp32 array that receives the sum over heads and columns of the squares of what is stored
   const __nv_bfloat16* residual;
   float* row_sumsq;
+  long long total_kv;    // rows of K / V (bounds the sequence ranges read from the offsets)
+  int kv_batch;          // sequences the KV offsets describe (bounds kv_index entries)
 };
 
 struct NormArgs {
@@ -130,6 +132,7 @@ struct BwdArgs {
   int window;          // band |q - kv| <= window of sequence-local positions; -1 = none
   float* dk_acc;       // start / end offsets: fp32 accumulators the dK / dV tiles are added into (else null)
   float* dv_acc;
+  long long total_kv;  // rows of K / V (bounds the sequence ranges read from the offsets)
 };
 
 struct BwdLaunch {
@@ -151,7 +154,15 @@ struct SchedArgs {
   int* sched;
   long long capacity_items;
   const void* kv_index;  // optional: sequence -> entry of the KV offsets
+  int kv_batch;          // sequences the KV offsets describe (bounds kv_index entries)
 };
+
+}  // namespace gdpa
+struct GdpaFwdParams;
+namespace gdpa {
+// Host-side argument checks of the forward entry points (no CUDA call): the return code gdpa_fwd / gdpa_fwd_fp8 would
+// give for these parameters before they launch anything (`needs_schedule`: a null schedule pointer is an error).
+int fwd_check_params(const GdpaFwdParams* p, bool fp8, bool needs_schedule);
 
 int launch_fwd_bf16(const FwdLaunch& l, int head_dim, int act_class);
 int launch_fwd_softmax_bf16(const FwdLaunch& l, int head_dim);

@@ -13,6 +13,8 @@
 //    threads) race on the array; callers must order them.
 //  - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
 //    sets the kernels' shared-memory attribute.  Make that first call outside any stream capture.
+//    The address is cached for the life of the process: after cudaDeviceReset() on that device the
+//    cached value is stale and this entry point must not be used again in the process.
 //  - No cudaMalloc / cudaFree / allocating library routine is called, on any path.
 #include <atomic>
 #include <mutex>
@@ -57,13 +59,16 @@ using namespace gdpa;
 
 #pragma GCC visibility push(default)
 extern "C" int gdpa_fwd_noalloc(const GdpaFwdParams* p, gdpa_stream_t stream) {
-  if (p == nullptr || p->struct_size != sizeof(GdpaFwdParams)) return GDPA_ERR_BAD_ARG;
-  if (p->batch < 0 || p->heads <= 0 || p->total_q < 0) return GDPA_ERR_BAD_ARG;
+  // The same host-side checks as gdpa_fwd, first: a call that gdpa_fwd would refuse must not have touched the
+  // shared array (nor launched anything) by the time it is refused.
+  int rc = fwd_check_params(p, false, false);
+  if (rc != GDPA_OK) return rc;
+  if (p->total_q == 0 || p->batch == 0) return GDPA_OK;
   // Upper bound on the number of work items, the same arithmetic gdpa_schedule_bytes() uses.
   const long long need = static_cast<long long>(p->heads) * (p->total_q / kFwdQBlock + p->batch);
   if (need > kNoallocMaxItems) return GDPA_ERR_NOALLOC_TOO_LARGE;
   int* sched = nullptr;
-  int rc = noalloc_schedule_ptr(&sched);
+  rc = noalloc_schedule_ptr(&sched);
   if (rc != GDPA_OK) return rc;
 
   GdpaSchedParams sp;
@@ -76,14 +81,12 @@ extern "C" int gdpa_fwd_noalloc(const GdpaFwdParams* p, gdpa_stream_t stream) {
   sp.heads = p->heads;
   sp.max_seq_len_q = p->max_seq_len_q;
   sp.max_seq_len_kv = p->max_seq_len_kv;
-  sp.reserved = 0;
+  sp.kv_batch = p->kv_batch;
   sp.schedule = sched;
   sp.schedule_bytes = static_cast<int64_t>(sizeof(int)) * (kSchedHeaderInts + 4 * kNoallocMaxItems);
   sp.kv_seq_index = p->kv_seq_index;
-  if (p->batch > 0 && p->total_q > 0) {
-    rc = gdpa_build_schedule(&sp, stream);
-    if (rc != GDPA_OK) return rc;
-  }
+  rc = gdpa_build_schedule(&sp, stream);
+  if (rc != GDPA_OK) return rc;
   GdpaFwdParams fp = *p;
   fp.schedule = sched;
   return gdpa_fwd(&fp, stream);

@@ -19,7 +19,11 @@ __device__ __forceinline__ void seq_geometry(const SchedArgs& a, int b, int& nbl
   long long s0, e0;
   seq_bounds(a.q_off, b, a.off64, s0, e0);
   long long lq = e0 - s0;
-  const int kb = a.kv_index != nullptr ? static_cast<int>(load_offset(a.kv_index, b, a.off64)) : b;
+  int kb = b;
+  if (a.kv_index != nullptr) {  // an entry beyond the KV batch is clamped, as the kernels do
+    kb = static_cast<int>(load_offset(a.kv_index, b, a.off64));
+    kb = kb < 0 ? 0 : (kb >= a.kv_batch ? a.kv_batch - 1 : kb);
+  }
   seq_bounds(a.kv_off, kb, a.off64, s0, e0);
   long long lkv = e0 - s0;
   lq = lq < 0 ? 0 : (lq < a.max_q ? lq : a.max_q);

@@ -21,6 +21,7 @@ enum : int {
   ST_ROLE_ACT = 3,
   ST_ROLE_EPI = 4,
   ST_ROLE_RED = 5,
+  ST_ROLE_FIX = 6,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -62,7 +63,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Bounded wait.  Returns false if the wait ran out or another role already gave up; in the first
-// case it records `code` in *abort_flag (shared) and in *status (global, may be null).
+// case it records `code` in *abort_flag (shared) and in *status (device memory or mapped host memory, may be null).
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                                 int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -75,7 +76,9 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
       if (t0 == 0) t0 = now;
       if (now - t0 > limit_ns) {
         *abort_flag = code;
-        if (status != nullptr) atomicCAS(status, 0, code);
+        // first writer wins, approximately: a plain test and store, because the word may live in pinned host memory
+        // mapped into the device's address space, where a device-scope atomic is not one
+        if (status != nullptr && *reinterpret_cast<volatile int*>(status) == 0) *reinterpret_cast<volatile int*>(status) = code;
         return false;
       }
     }

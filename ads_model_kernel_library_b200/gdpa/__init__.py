@@ -10,6 +10,7 @@ from .ops import (  # noqa: F401
     kernel_status,
     kernel_timing,
     quantize_fp8_blockwise,
+    set_offset_validation,
 )
 from .sharding import gather_rows, max_over_ranks, plan_token_balanced_shards, shard_inputs, shard_jagged  # noqa: F401
 from .workloads import WORKLOADS, make_workload, useful_flops  # noqa: F401

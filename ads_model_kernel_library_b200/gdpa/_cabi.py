@@ -1,7 +1,9 @@
 """ctypes binding of libgdpa_b200.so (C ABI declared in include/gdpa_b200.h).
 
-The library is the only compute path of this package: if it is missing or cannot be loaded,
-importing this module raises -- there is no fallback.
+The library is the only compute path of this package.  It is loaded on first use of ``_cabi.lib``
+(so that host-only helpers such as the workload generators and the shard planner can be imported in a
+process that never touches the GPU); if it is missing or cannot be loaded, that first use raises --
+there is no fallback.  ``GDPA_B200_LIB`` overrides the path (a differently built copy of the library).
 """
 from __future__ import annotations
 
@@ -9,7 +11,7 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG, "libgdpa_b200.so")
+LIB_PATH = os.environ.get("GDPA_B200_LIB") or os.path.join(_PKG, "libgdpa_b200.so")
 
 # Return codes, activation ids and enums of include/gdpa_b200.h
 GDPA_OK = 0
@@ -53,7 +55,7 @@ class GdpaSchedParams(C.Structure):
         ("heads", C.c_int32),
         ("max_seq_len_q", C.c_int32),
         ("max_seq_len_kv", C.c_int32),
-        ("reserved", C.c_int32),
+        ("kv_batch", C.c_int32),
         ("schedule", C.c_void_p),
         ("schedule_bytes", C.c_int64),
         ("kv_seq_index", C.c_void_p),
@@ -98,6 +100,8 @@ class GdpaFwdParams(C.Structure):
         ("v_strides", C.c_int64 * 2),
         ("residual", C.c_void_p),
         ("row_sumsq", C.c_void_p),
+        ("kv_batch", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -260,9 +264,15 @@ def _load() -> C.CDLL:
     return lib
 
 
-lib = _load()
+def __getattr__(name):
+    # PEP 562: `_cabi.lib` is created by its first use and is an ordinary module attribute afterwards
+    if name == "lib":
+        globals()["lib"] = _load()
+        return globals()["lib"]
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 def check(code: int, what: str) -> None:
     if code != GDPA_OK:
-        raise RuntimeError(f"{what}: {lib.gdpa_strerror(code).decode()} (code {code})")
+        handle = globals().get("lib") or __getattr__("lib")
+        raise RuntimeError(f"{what}: {handle.gdpa_strerror(code).decode()} (code {code})")

@@ -10,6 +10,7 @@ memory and streams only; all arithmetic runs in libgdpa_b200.so.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -52,25 +53,90 @@ def _set_timing(p, which: str) -> None:
         p.timing_stop_event = pair[1].cuda_event
 
 
+_ROLE_NAMES = {1: "TMA loader", 2: "MMA issuer", 3: "activation warps", 4: "epilogue", 5: "dQ reduce warps", 6: "tail fixer"}
+
+
+def _device_key(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
-    """Per-device int32 word the kernels write when one of their bounded waits runs out."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """Per-device int32 word the kernels write when one of their bounded waits runs out.  It lives in pinned host
+    memory, which the device addresses directly (unified addressing), so the host can look at it at any time
+    without synchronising; the kernels touch it only on that failure path."""
+    key = _device_key(device)
     t = _status_words.get(key)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
+        t = torch.zeros(1, dtype=torch.int32).pin_memory()
         _status_words[key] = t
     return t
 
 
+def _describe_status(code: int) -> str:
+    return (f"a kernel wait ran out (status 0x{code:x}: barrier {code >> 8}, role {_ROLE_NAMES.get(code & 0xff, code & 0xff)}); "
+            "results of the calls since the last check on this device are incomplete")
+
+
+def _raise_if_wait_ran_out(device: torch.device) -> None:
+    """Called at the start of every operator call: if a kernel of an EARLIER call on this device gave up on a wait,
+    raise now (and clear the word).  A plain host read, no synchronisation."""
+    t = _status_words.get(_device_key(device))
+    if t is not None:
+        code = int(t[0])
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(_describe_status(code))
+
+
 def kernel_status(device=None) -> int:
-    """Read (and clear) the kernels' status word of a device: 0 = every wait completed.
-    Synchronises the device; meant for tests and diagnostics, not for the hot path."""
+    """Synchronise the device, then read (and clear) its status word: 0 = every wait of every kernel launched so
+    far completed.  For tests and diagnostics; the operator itself checks the word, without synchronising, at the
+    start of the next call on the device."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     t = _status_word(device)
-    v = int(t.item())
+    torch.cuda.synchronize(device)
+    v = int(t[0])
     if v != 0:
         t.zero_()
     return v
+
+
+_validate_offsets = os.environ.get("GDPA_CHECK_OFFSETS", "0") not in ("", "0")
+
+
+def set_offset_validation(enabled: bool) -> bool:
+    """Switch the host-side check of the offset arrays on or off (default: the environment variable
+    ``GDPA_CHECK_OFFSETS=1``, else off); returns the previous setting.  When on, every operator call copies its
+    offset arrays to the host (a synchronisation) and raises ``ValueError`` before anything is launched if they are
+    not non-negative, non-decreasing and inside the tensors.  When off the arrays are trusted, as the reference
+    trusts them; the kernels then only guarantee that they do not access memory outside the tensors."""
+    global _validate_offsets
+    old, _validate_offsets = _validate_offsets, bool(enabled)
+    return old
+
+
+def _check_offsets(name: str, off: torch.Tensor, rows: int, start_end: bool) -> None:
+    o = off.detach().to("cpu", torch.int64)
+    if o.numel() == 0:
+        return
+    if int(o.min()) < 0 or int(o.max()) > rows:
+        raise ValueError(f"{name} has entries outside [0, {rows}] (the rows of its tensor)")
+    if start_end:
+        if bool((o[1::2] < o[0::2]).any()):
+            raise ValueError(f"{name} holds a [start, end] pair with end < start")
+    elif bool((o[1:] < o[:-1]).any()):
+        raise ValueError(f"{name} must be non-decreasing (exclusive prefix sums of the sequence lengths)")
+
+
+def _maybe_validate(qo, ko, total_q: int, total_kv: int, start_end: bool = False, kv_index=None) -> None:
+    if not _validate_offsets:
+        return
+    _check_offsets("query_offset", qo, total_q, start_end)
+    _check_offsets("key_offset", ko, total_kv, start_end)
+    if kv_index is not None and kv_index.numel() > 0:
+        idx = kv_index.detach().to("cpu", torch.int64)
+        if int(idx.min()) < 0 or int(idx.max()) >= ko.numel() - 1:
+            raise ValueError("ad_to_request_offset has entries outside [0, number of KV sequences)")
 
 
 def _stream_ptr() -> C.c_void_p:
@@ -78,6 +144,8 @@ def _stream_ptr() -> C.c_void_p:
 
 
 def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False, start_end: bool = False) -> Tuple[int, int, int]:
+    if q.is_cuda:
+        _raise_if_wait_ran_out(q.device)
     for name, t in (("query", q), ("key", k), ("value", v)):
         if t.dim() != 3:
             raise ValueError(f"{name} must be [total_tokens, H, D], got {tuple(t.shape)}")
@@ -109,9 +177,10 @@ def _check_inputs(q, k, v, qo, ko, dtype, shared_kv: bool = False, start_end: bo
             raise ValueError(f"{name} must be contiguous")
     if qo.dtype != ko.dtype or (qo.numel() != ko.numel() and not shared_kv):
         raise ValueError("query_offset and key_offset must have the same length and dtype")
+    if start_end and qo.numel() % 2 != 0:
+        raise ValueError("start / end offsets hold two entries per sequence")
+    _maybe_validate(qo, ko, q.shape[0], k.shape[0], start_end)
     if start_end:
-        if qo.numel() % 2 != 0:
-            raise ValueError("start / end offsets hold two entries per sequence")
         return qo.numel() // 2, H, D
     return qo.numel() - 1, H, D
 
@@ -138,6 +207,7 @@ def _build_schedule(mode: int, qo, ko, batch: int, heads: int, total_rows: int, 
     p.schedule_bytes = sched.numel() * 4
     if kv_index is not None:
         p.kv_seq_index = kv_index.data_ptr()
+        p.kv_batch = ko.numel() - 1
     _cabi.check(_cabi.lib.gdpa_build_schedule(C.byref(p), _stream_ptr()), "gdpa_build_schedule")
     return sched
 
@@ -372,6 +442,7 @@ def _gdpa_forward_shared_kv_op(
     if kv_seq_index.numel() != batch or kv_seq_index.device != query.device:
         raise ValueError("ad_to_request_offset must hold one KV sequence index per Q sequence, on the device of query")
     kv_index = kv_seq_index.to(query_offset.dtype).contiguous()
+    _maybe_validate(query_offset, key_offset, query.shape[0], key.shape[0], kv_index=kv_index)
     with torch.cuda.device(query.device):
         o = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         if query.shape[0] == 0 or batch == 0:
@@ -381,6 +452,7 @@ def _gdpa_forward_shared_kv_op(
         p = _fill_fwd_params(query, key, value, o, query_offset, key_offset, batch, H, D, max_seq_len_q,
                              max_seq_len_kv, qk_scale, activation, sched, _cabi.GDPA_DTYPE_BF16)
         p.kv_seq_index = kv_index.data_ptr()
+        p.kv_batch = key_offset.numel() - 1
         p.window_plus_one = window_size + 1 if window_size >= 0 else 0
         _set_timing(p, "fwd")
         _cabi.check(_cabi.lib.gdpa_fwd(C.byref(p), _stream_ptr()), "gdpa_fwd")
@@ -623,6 +695,11 @@ def _broadcast_query(query, query_offset, key_offset, output_offset):
         output_offset = torch.arange(batch + 1, device=query.device, dtype=key_offset.dtype) * lq
     elif output_offset.numel() != batch + 1:
         raise ValueError("output_offset must have one entry per KV sequence plus one")
+    elif _validate_offsets or not output_offset.is_cuda:
+        # a device tensor is compared only when offset validation is on (the comparison synchronises)
+        dense = torch.arange(batch + 1, dtype=torch.int64) * lq
+        if not torch.equal(output_offset.detach().to("cpu", torch.int64), dense):
+            raise ValueError("output_offset must be the dense layout [0, Lq, 2 Lq, ...]")
     return query.repeat(batch, 1, 1), output_offset.to(key_offset.dtype).contiguous()
 
 

@@ -1,0 +1,126 @@
+#!/usr/bin/env python
+"""Same-box comparator: the reference's own Blackwell GDPA kernels (CuteDSL, `flash_attn_varlen_func`,
+gdpa/src/interface.py:2223 of the reference) timed on the cells of the reference's published workload
+(gdpa/scripts/benchmark.py:176-185, :574-598), the way that script times them (`run_fwd` :239-265, `run_bwd`
+:330-385: tile maps precomputed outside the timed call, backward through autograd with retain_graph).
+
+    baseline/install_reference.sh /path/to/ads_model_kernel_library      # once, where the reference is mounted
+    python baseline/reference_gpu_arm.py [--small-only] [--sets self_s1,...] [--lengths 256,...]
+
+The reference's kernels are Python DSL sources that compile at their first call, against the nvidia-cutlass-dsl
+package of the machine (the reference pins another version), and their waits have no time limit.  So every cell
+runs in a child process with a time limit; the first cell is a small one (B=8, L=512); the first failure or
+time-out ends the run and is reported as one JSON line with `"unavailable"`.  One JSON line per cell otherwise.
+This arm is a reported comparison; nothing in the package or in the tests depends on it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+
+
+def worker(kind: str, L: int, B: int, mode: str, cell_ms: float) -> None:
+    import numpy as np
+    import torch
+
+    sys.path.insert(0, REF)
+    from ads_mkl.ops.oss.gdpa.src.interface import flash_attn_varlen_func, precompute_for_varline_load_balancing
+
+    torch.manual_seed(2025)
+    H, D = 4, 128
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(2025 + L)
+    lq = rng.integers(1, L + 1, B) if kind == "self_s05" else np.full(B, L)
+    dff = 256 if kind == "cross_kv256" else L
+    q_off = torch.from_numpy(np.concatenate([[0], np.cumsum(lq)])).to(torch.int32).to(dev)
+    kv_off = (torch.arange(B + 1, dtype=torch.int32) * dff).to(dev)
+    grad = mode == "bwd"
+    q = torch.randn(int(lq.sum()), H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+    k = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+    v = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+    tq = precompute_for_varline_load_balancing(q, q_off, kv_off)
+    kw = dict(q=q, k=k, v=v, cu_seqlens_q=q_off, cu_seqlens_k=kv_off, max_seqlen_q=int(lq.max()), max_seqlen_k=dff,
+              prefer_persistent=True, tile_to_batch_q=tq[0], tile_to_head_q=tq[1], tile_to_block_q=tq[2], activation="fast_gelu")
+    if grad:
+        tk = precompute_for_varline_load_balancing(q, q_off, kv_off, is_bwd=True)
+        kw.update(tile_to_batch_k=tk[0], tile_to_head_k=tk[1], tile_to_block_k=tk[2])
+    pairs = float((lq.astype(np.float64) * dff).sum())
+    flops = 4.0 * H * D * pairs * (2.5 if grad else 1.0)
+    if grad:
+        res = flash_attn_varlen_func(**kw)
+        out = res[0] if isinstance(res, (tuple, list)) else res
+        dout = torch.randn_like(out)
+
+        def fn():
+            q.grad = k.grad = v.grad = None
+            out.backward(dout, retain_graph=True)
+    else:
+        def fn():
+            with torch.no_grad():
+                flash_attn_varlen_func(**kw)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(); fn(); b.record(); torch.cuda.synchronize()
+    reps = int(min(200, max(5, cell_ms / max(a.elapsed_time(b), 1e-3))))
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for x, y in evs:
+        x.record(); fn(); y.record()
+    torch.cuda.synchronize()
+    ms = float(np.median([x.elapsed_time(y) for x, y in evs]))
+    print("RESULT " + json.dumps({"impl": "reference_kernel", "metric": f"gdpa_{mode}_useful_tflops", "value": flops / (ms * 1e-3) / 1e12,
+                                  "unit": "TFLOP/s", "ms_per_step": ms, "steps": reps,
+                                  "config": {"workload": f"ref_{kind}_{mode}_L{L}", "batch": B, "heads": H, "head_dim": D,
+                                             "activation": "fast_gelu", "api": "flash_attn_varlen_func (CuteDSL, persistent)"}}), flush=True)
+
+
+def run_cell(kind, L, B, mode, cell_ms, limit_s):
+    cmd = [sys.executable, os.path.abspath(__file__), "--worker", kind, str(L), str(B), mode, str(cell_ms)]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=limit_s)
+    except subprocess.TimeoutExpired:
+        return None, f"no result within {limit_s} s (compile or kernel did not finish)"
+    for line in r.stdout.splitlines():
+        if line.startswith("RESULT "):
+            return json.loads(line[7:]), None
+    tail = (r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["no output"])[-1]
+    return None, f"exit code {r.returncode}: {tail[:400]}"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--worker", nargs=5, default=None)
+    ap.add_argument("--small-only", action="store_true")
+    ap.add_argument("--sets", default="self_s1,self_s05,cross_kv256")
+    ap.add_argument("--lengths", default="256,512,1024,2048")
+    ap.add_argument("--cell-ms", type=float, default=600.0)
+    ap.add_argument("--limit-s", type=float, default=300.0)
+    args = ap.parse_args()
+    if args.worker:
+        kind, L, B, mode, cell_ms = args.worker
+        worker(kind, int(L), int(B), mode, float(cell_ms))
+        return
+    if not os.path.isdir(os.path.join(REF, "ads_mkl", "ops", "oss", "gdpa")):
+        print(json.dumps({"impl": "reference_kernel", "unavailable": "baseline/_ref is empty: run baseline/install_reference.sh first"}))
+        return
+    cells = [("self_s1", 512, 8, "fwd"), ("self_s1", 512, 8, "bwd")]
+    if not args.small_only:
+        order = [("self_s1", 2048)] + [(k, int(L)) for k in args.sets.split(",") for L in args.lengths.split(",") if (k, int(L)) != ("self_s1", 2048)]
+        cells += [(k, L, 1152, mode) for k, L in order for mode in ("fwd", "bwd")]
+    for kind, L, B, mode in cells:
+        res, err = run_cell(kind, L, B, mode, args.cell_ms, args.limit_s)
+        if res is None:
+            print(json.dumps({"impl": "reference_kernel", "unavailable": f"ref_{kind}_{mode}_L{L} (B={B}): {err}"}), flush=True)
+            return
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

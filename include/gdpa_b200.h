@@ -30,6 +30,12 @@
  *  - Every in-kernel wait is bounded.  A wait that runs out writes a non-zero code to
  *    `status` (if given), the kernel frees its tensor memory and returns; the context stays
  *    usable.
+ *  - Offsets are trusted to be monotone prefix sums inside the tensors.  The kernels clamp every sequence range
+ *    they read from an offset array to [0, total_q] / [0, total_kv], so a malformed array gives unspecified values
+ *    for the sequences concerned but no access outside the tensors; checking the arrays is the host's business.
+ *  - A sequence's result depends on that sequence's rows only: rows of other sequences that share a 128-row tile
+ *    with it never reach its output, whatever they hold (Inf and NaN included), as with the reference's
+ *    zero-padded per-sequence loads.
  */
 #ifndef GDPA_B200_H_
 #define GDPA_B200_H_
@@ -102,13 +108,13 @@ typedef struct GdpaSchedParams {
   int32_t heads;
   int32_t max_seq_len_q;      /* lengths are clamped to these, as the reference does          */
   int32_t max_seq_len_kv;     /*   (gdpa/triton/triton_generalized_dot_product_attention.py:599-624) */
-  int32_t reserved;
+  int32_t kv_batch;           /* with kv_seq_index: sequences kv_offsets describes (its entries - 1); 0 = batch */
   void* schedule;             /* out: gdpa_schedule_bytes() bytes, 16-byte aligned             */
   int64_t schedule_bytes;     /* size of that buffer                                           */
   /* Optional [batch] map from a Q sequence to the entry of kv_offsets it attends to (the reference's
    * ad_to_request_offset: many Q sequences share one KV sequence, forward / inference only;
    * gdpa/triton/triton_generalized_dot_product_attention.py:3961-3966).  Same integer type as the
-   * offsets.  Null = sequence b reads KV sequence b. */
+   * offsets.  Null = sequence b reads KV sequence b.  Entries outside [0, kv_batch) are clamped into it. */
   const void* kv_seq_index;
 } GdpaSchedParams;
 
@@ -147,7 +153,9 @@ typedef struct GdpaFwdParams {
   int32_t activation;         /* GDPA_ACT_* */
   float qk_scale;             /* multiplies act(S); for softmax multiplies S before exp */
   const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_FWD) */
-  int32_t* status;            /* optional device int32, written non-zero if a wait ran out */
+  int32_t* status;            /* optional int32 in device memory, or in pinned host memory mapped into the device's
+                                 address space (the host can then poll it without a synchronisation); written
+                                 non-zero if a wait ran out */
   /* FP8 path only (gdpa_fwd_fp8): one fp32 scale per (sequence-local 128-token block, head),
    * laid out [number of blocks over the batch, heads]; block b of sequence s sits at row
    * block_offsets[s] + b where block_offsets is the exclusive prefix sum of ceil(len / 128). */
@@ -192,6 +200,10 @@ typedef struct GdpaFwdParams {
    * then turns into the RMS norm over heads * head_dim (:359-405).  Null = plain O. */
   const void* residual;
   float* row_sumsq;
+  /* With kv_seq_index: the number of sequences kv_offsets describes (its entries minus one); entries of
+   * kv_seq_index outside [0, kv_batch) are clamped into it.  0 = batch. */
+  int32_t kv_batch;
+  int32_t reserved;
 } GdpaFwdParams;
 
 int gdpa_fwd(const GdpaFwdParams* params, gdpa_stream_t stream);

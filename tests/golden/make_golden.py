@@ -21,6 +21,12 @@ symlink of that name makes them resolve.  Four things are recorded:
   of the table; plus one grouped-query case (4 query heads, 2 K/V heads), one banded case
   (``window_size = 6``), one case with per-head activations (``ensemble_activation_list``), one with
   ``broadcast_q`` and one with ``use_start_end_offsets`` (overlapping K / V ranges).  These pin where the scale is applied and every gradient;
+* ``norms_{rms,ln_rms}_ref``: the expected values of the reference's two GDPA-plus-norm tests
+  (gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:50-91 RMS norm after GDPA; :93-145 layer norm of Q, GDPA,
+  Q residual, RMS norm), computed by the reference's own statements: the input generator
+  ``_make_dense_jagged_inputs``, ``_gdpa_reference`` and the assignments to ``ln_q``, ``gdpa_ref`` and ``ref`` are
+  taken from the test file by ``ast`` and executed unchanged on the CPU with the test's seed, shape and dtype
+  (bf16; the kernel call itself needs a Triton fork and a GPU and is left out);
 * ``activation_ids.json``: the reference's activation name -> id table (gdpa/triton/math.py:77-78).
 
 Outputs: ``gdpa_golden.npz`` and ``activation_ids.json`` beside this script.
@@ -185,6 +191,31 @@ def main(ref_root: str) -> None:
     ose[~covered] = 0  # rows no sequence owns are uninitialised memory in the reference's output (torch.empty, :3015)
     out.update(startend_q_pairs=q_pairs.numpy(), startend_k_pairs=k_pairs.numpy(), startend_o=ose.numpy(),
                startend_dq=rese[0].float().numpy(), startend_dk=rese[1].float().numpy(), startend_dv=rese[2].float().numpy())
+
+    # ---- 4. the expected values of the reference's GDPA-plus-norm tests, by the tests' own statements ----------
+    make_inputs = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "_make_dense_jagged_inputs")
+    cls = next(n for n in tree.body if isinstance(n, ast.ClassDef) and n.name == "TLXGDPAMegakernelTest")
+    for method, tag in (("test_fused_rmsnorm_matches_reference", "rms"),
+                        ("test_fused_layernorm_and_rmsnorm_matches_reference", "ln_rms")):
+        body = next(n for n in cls.body if isinstance(n, ast.FunctionDef) and n.name == method).body
+        wanted = {"dtype", "activation", "normalized_shape", "ln_q", "gdpa_ref", "ref"}
+        stmts = [st for st in body if isinstance(st, ast.Assign) and len(st.targets) == 1
+                 and isinstance(st.targets[0], ast.Name) and st.targets[0].id in wanted]
+        seed = next(st for st in body if isinstance(st, ast.Expr) and "manual_seed" in ast.unparse(st))
+        inputs = next(st for st in body if isinstance(st, ast.Assign) and "_make_dense_jagged_inputs" in ast.unparse(st))
+        ns4 = {"torch": torch, "get_pytorch_activation": ref_math.get_pytorch_activation, "device": "cpu"}
+        exec(compile(ast.Module(body=[make_inputs, fn], type_ignores=[]), src_path, "exec"), ns4)
+        order = sorted([seed, inputs] + stmts, key=lambda st: st.lineno)
+        exec(compile(ast.Module(body=order, type_ignores=[]), src_path, "exec"), ns4)
+        assert ns4["dtype"] == torch.bfloat16 and ns4["q"].shape == (256, 2, 128)
+        # bf16 values are stored as their 16 bits; both tests draw the same inputs (same seed, same calls)
+        bits = lambda t: t.contiguous().view(torch.int16).numpy()
+        for name in ("q", "k", "v"):
+            if f"norms_{name}_bf16_bits" in out:
+                assert np.array_equal(out[f"norms_{name}_bf16_bits"], bits(ns4[name]))
+            out[f"norms_{name}_bf16_bits"] = bits(ns4[name])
+        out[f"norms_{tag}_ref_bf16_bits"] = bits(ns4["ref"])
+        out["norms_offsets"] = ns4["offsets"].numpy()
 
     np.savez_compressed(os.path.join(HERE, "gdpa_golden.npz"), **out)
     ids = {a.value: i for a, i in ref_math.activation_to_int.items()}

@@ -91,3 +91,78 @@ def test_full_forward_configuration_sampled_parity(G):
     cost = w.q_lens * w.kv_lens
     order = np.argsort(cost)
     _sample_check(G, w, t, o, None, w.activation, [int(i) for i in order[:3]] + [int(order[len(order) // 2]), int(order[-1])])
+
+
+def test_full_fp8_softmax_configuration_sampled_parity(G):
+    """B=1024, H=4, D=128, L ~ U[128, 2048], FP8 e4m3 inputs with per-128-token-block scales, softmax, scale
+    1/sqrt(D), bf16 output: the whole batch in one launch; the three shortest sequences, a median and the longest
+    one against the oracle on their DE-QUANTISED inputs, at the stated FP8 bound (atol 5e-2, rtol 1e-1, at most
+    1 % of the elements outside)."""
+    from ads_model_kernel_library_b200.gdpa.workloads import make_tensors, make_workload
+
+    w = make_workload("c4_fp8_softmax")
+    t = make_tensors(w, torch.device("cuda"), seed=9, dtype=torch.float32)
+    qo = t["q_offsets"]
+    q8, sq, qb = G.quantize_fp8_blockwise(t["q"], qo)
+    k8, sk, kb = G.quantize_fp8_blockwise(t["k"], qo)
+    v8, sv, vb = G.quantize_fp8_blockwise(t["v"], qo)
+    mx = int(w.q_lens.max())
+    o = G.generalized_dot_product_attention_fp8(q8, k8, v8, sq, sk, sv, qb, kb, qo, qo, mx, mx, qk_scale=w.qk_scale,
+                                                activation="softmax")
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0 and o.dtype == torch.bfloat16 and torch.isfinite(o.float()).all()
+    # repeatability: the forward has no atomics
+    o2 = G.generalized_dot_product_attention_fp8(q8, k8, v8, sq, sk, sv, qb, kb, qo, qo, mx, mx, qk_scale=w.qk_scale,
+                                                 activation="softmax")
+    assert torch.equal(o, o2)
+    off, boff = qo.cpu(), qb.cpu()
+
+    def deq(x8, s, b):
+        r0, r1, b0 = int(off[b]), int(off[b + 1]), int(boff[b])
+        rows = x8[r0:r1].float().cpu()
+        blk = torch.arange(r1 - r0) // 128 + b0
+        return rows * s.cpu()[blk].unsqueeze(-1)
+
+    order = np.argsort(w.q_lens)
+    worst = 0.0
+    for b in [int(i) for i in order[:3]] + [int(order[len(order) // 2]), int(order[-1])]:
+        n = int(w.q_lens[b])
+        one = torch.tensor([0, n])
+        ref = orc.gdpa_forward(deq(q8, sq, b), deq(k8, sk, b), deq(v8, sv, b), one, one, "softmax", w.qk_scale)
+        got = o[int(off[b]):int(off[b + 1])].float().cpu()
+        err = (got - ref).abs()
+        outside = (err > 5e-2 + 1e-1 * ref.abs()).float().mean().item()
+        worst = max(worst, float(err.max()))
+        assert outside <= 0.01, f"sequence {b} (length {n}): {outside:.4f} of the elements outside the FP8 bound"
+    assert worst < 0.25  # softmax outputs are averages of N(0,1) values: errors stay far below one
+
+
+def test_full_zipf_shard_sampled_parity(G):
+    """One token-balanced shard (1/8) of the B=8192 Zipf(1.2) configuration (H=4, D=128, lengths 32 ... 8192,
+    GELU-tanh, scale 1/8192), forward and backward in one launch each, as a rank of the 8-GPU split runs it; the three
+    shortest sequences, a median one and one at the 8 192-token cap against the fp32 oracle."""
+    from ads_model_kernel_library_b200.gdpa.sharding import plan_token_balanced_shards
+    from ads_model_kernel_library_b200.gdpa.workloads import make_tensors, make_workload
+
+    w = make_workload("c5_zipf_sharded")
+    s, e = plan_token_balanced_shards(w.q_lens, w.kv_lens, 8)[0]
+    t = make_tensors(w, torch.device("cuda"), seed=10, with_grad_out=True, seq_range=(s, e))
+    lens = w.q_lens[s:e]
+    mq = int(lens.max())
+    assert mq == 8192
+    q, k, v = (t[n].requires_grad_(True) for n in ("q", "k", "v"))
+    o = G.generalized_dot_product_attention(q, k, v, t["q_offsets"], t["kv_offsets"], mq, mq, qk_scale=w.qk_scale,
+                                            activation=w.activation)
+    o.backward(t["do"])
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    for x in (o, q.grad, k.grad, v.grad):
+        assert torch.isfinite(x.float()).all()
+    order = np.argsort(lens, kind="stable")
+    sample = [int(i) for i in order[:3]] + [int(order[len(order) // 2]), int(order[-1])]
+
+    class W:  # the fields _sample_check reads
+        qk_scale = w.qk_scale
+
+    tt = {n: t[n].detach() for n in ("q", "k", "v", "do", "q_offsets", "kv_offsets")}
+    _sample_check(G, W, tt, o.detach(), (q.grad, k.grad, v.grad), w.activation, sample)

@@ -502,3 +502,64 @@ def test_start_end_offsets_argument_errors(G):
         G.generalized_dot_product_attention(q, q, q, torch.tensor([0, 4, 8], device="cuda"),
                                             torch.tensor([0, 4, 8], device="cuda"), 8, 8, use_start_end_offsets=True,
                                             total_num_objects=8)  # an odd number of entries
+
+
+def test_config5_longest_sequences_against_the_oracle(G):
+    """The sharded Zipf configuration at its real lengths (H=4, D=128, GELU-tanh, scale 1/8192): one sequence at the
+    8 192-token cap (64 KV tiles, 32 forward Q blocks: the heaviest bins of the schedule), one of 8 160 tokens (ragged
+    last tile) and short ones in the same batch, forward and backward against the fp32 oracle."""
+    ln = np.array([32, 8192, 96, 8160, 64, 544, 32, 1024], dtype=np.int64)
+    cpu, dev = jagged_inputs(ln, ln, 4, 128, seed=56, std=0.5)
+    scale = 1.0 / 8192
+    o, dq, dk, dv = run_fwd_bwd(G, dev, ln, ln, "gelu_approx", scale)
+    ro, rdq, rdk, rdv = oracle_forward_backward(cpu, "gelu_approx", scale)
+    for a, b, n in ((o, ro, "O"), (dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_close(a, b, n)
+
+
+def test_offset_validation_is_opt_in_and_raises_before_any_launch(G):
+    """With validation on, malformed offset arrays raise ValueError and nothing is launched; well-formed ones pass."""
+    from ads_model_kernel_library_b200.gdpa import _cabi
+
+    lq, lk = [100, 37], [64, 200]
+    cpu, dev = jagged_inputs(lq, lk, 2, 64, seed=3, std=0.5)
+    old = G.set_offset_validation(True)
+    try:
+        n0 = _cabi.lib.gdpa_launch_count()
+        beyond = dev["qo"].clone(); beyond[-1] += 5            # last entry past the rows of the tensor
+        down = dev["ko"].clone(); down[1] = down[2] + 1        # not monotone
+        neg = dev["qo"].clone(); neg[0] = -1
+        for qo, ko in ((beyond, dev["ko"]), (dev["qo"], down), (neg, dev["ko"])):
+            with pytest.raises(ValueError):
+                G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], qo, ko, 100, 200, activation="relu")
+        with pytest.raises(ValueError):  # KV sequence index out of range
+            G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 100, 200, activation="relu",
+                                                ad_to_request_offset=torch.tensor([0, 2], device="cuda"))
+        assert _cabi.lib.gdpa_launch_count() == n0
+        o = G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 100, 200, qk_scale=0.1,
+                                                activation="relu")
+        assert_close(o, oracle_forward(cpu, "relu", 0.1), "O with validation on")
+    finally:
+        G.set_offset_validation(old)
+
+
+def test_timed_out_wait_is_raised_by_the_next_operator_call(G):
+    """The kernels' status word lives in pinned host memory: a wait that runs out (here the probe kernel's, with a
+    20 ms limit, writing to the operator's own word) is reported by the next operator call on the device without
+    anyone asking, and the call after that works."""
+    import ctypes as C
+
+    from ads_model_kernel_library_b200.gdpa import _cabi, ops
+
+    cpu, dev = jagged_inputs([100], [100], 1, 64, seed=2, std=0.5)
+    word = ops._status_word(dev["q"].device)
+    assert word.is_pinned() and int(word[0]) == 0
+    rc = _cabi.lib.gdpa_debug_wait_probe(C.c_void_p(word.data_ptr()), 20_000_000,
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(word[0]) == (0x7700 | 1)  # written by the device straight into host memory
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 100, 100, activation="relu")
+    o = run_fwd(G, dev, [100], [100], "relu", 0.1)  # the word was cleared by the raise
+    assert_close(o, oracle_forward(cpu, "relu", 0.1), "O after a reported time-out")

@@ -150,3 +150,25 @@ def test_norm_pipeline_backward_against_autograd_of_the_oracle(G, case):
         # weight / bias gradients are sums over all tokens: compare relative to their scale
         tol = NORM_ATOL * max(1.0, float(want.abs().max()))
         assert_close(got, want, f"d {name}[{case}]", atol=tol, rtol=NORM_RTOL)
+
+
+def test_pipeline_reproduces_the_reference_tests_expected_values(G, golden):
+    """The two cases of the reference's own GDPA-plus-norm test file on the reference's own inputs, against the
+    expected tensors its statements produce (fixture generated by tests/golden/make_golden.py from the reference's
+    source), at the reference's tolerance atol = rtol = 3e-2
+    (gdpa_megakernel/tests/test_tlx_gdpa_megakernel.py:91, :145)."""
+    bf = lambda n: torch.from_numpy(golden[n]).view(torch.bfloat16)
+    q, k, v = (bf(f"norms_{n}_bf16_bits").cuda() for n in ("q", "k", "v"))
+    off = torch.from_numpy(golden["norms_offsets"]).cuda()
+    out = G.tlx_gdpa_megakernel(query=q, key=k, value=v, query_offset=off, key_offset=off, max_seq_len_q=128,
+                                max_seq_len_kv=128, activation="fast_gelu", enable_tma=True, enable_ws=True,
+                                fused_rms_norm=True)
+    torch.cuda.synchronize()
+    assert G.kernel_status() == 0
+    assert_close(out, bf("norms_rms_ref_bf16_bits").float(), "RMS norm after GDPA", atol=NORM_ATOL, rtol=NORM_RTOL)
+    out = G.tlx_gdpa_megakernel(query=q, key=k, value=v, query_offset=off, key_offset=off, max_seq_len_q=128,
+                                max_seq_len_kv=128, activation="fast_gelu", enable_tma=True, enable_ws=True,
+                                fused_layernorm=True, fused_q_residual_add=True, fused_rms_norm=True)
+    torch.cuda.synchronize()
+    assert_close(out, bf("norms_ln_rms_ref_bf16_bits").float(), "layer norm, GDPA, residual, RMS norm", atol=NORM_ATOL,
+                 rtol=NORM_RTOL)

@@ -248,3 +248,26 @@ def test_mxfp8_restatement_round_trip(axis, D):
     if axis == 0:
         atom = sf[(0 * 5 + 1) * d_atoms * 512:(0 * 5 + 1) * d_atoms * 512 + 512].view(32, 4, 4)
         assert int(atom[2:, 0].sum()) == 0 and int(atom[:, 1:].sum()) == 0 and int(atom[:2, 0, :min(4, D // 32)].min()) > 0
+
+
+def _bf16(golden, name):
+    return torch.from_numpy(golden[name]).view(torch.bfloat16)
+
+
+def test_norm_pipeline_oracle_pinned_by_the_reference_tests_own_expected_values(golden):
+    """The expected tensors of the reference's two GDPA-plus-norm tests (gdpa_megakernel/tests/
+    test_tlx_gdpa_megakernel.py:50-91 and :93-145), computed by the reference's own statements (see make_golden.py),
+    against `gdpa_with_norms` on the same bf16 inputs.  The reference rounds its intermediate results to bf16 (the
+    GDPA output, the normalised Q); the oracle keeps fp32 except for the normalised Q, so the two agree to bf16
+    rounding of values of order one."""
+    q, k, v = (_bf16(golden, f"norms_{n}_bf16_bits") for n in ("q", "k", "v"))
+    off = torch.from_numpy(golden["norms_offsets"])
+    assert q.shape == (256, 2, 128) and off.tolist() == [0, 128, 256]
+    rms = orc.gdpa_with_norms(q, k, v, off, off, "fast_gelu", None, fused_rms_norm=True)
+    torch.testing.assert_close(rms, _bf16(golden, "norms_rms_ref_bf16_bits").float(), atol=2e-2, rtol=2e-2)
+    both = orc.gdpa_with_norms(q, k, v, off, off, "fast_gelu", None, fused_layernorm=True, fused_q_residual_add=True,
+                               fused_rms_norm=True, round_dtype=torch.bfloat16)
+    torch.testing.assert_close(both, _bf16(golden, "norms_ln_rms_ref_bf16_bits").float(), atol=2e-2, rtol=2e-2)
+    # mean absolute difference: far below one bf16 ulp of the values (order one), i.e. the same function
+    assert float((both - _bf16(golden, "norms_ln_rms_ref_bf16_bits").float()).abs().mean()) < 3e-3
+    assert float((rms - _bf16(golden, "norms_rms_ref_bf16_bits").float()).abs().mean()) < 3e-3
