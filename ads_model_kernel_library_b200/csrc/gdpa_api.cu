@@ -81,6 +81,17 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
   return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
 }
 
+// The five maps of one tensor (box heights kTmapRows), for zero-padded tile loads.
+int make_tmap_set(TmapSet* set, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
+                  int head_dim, int box_cols, long long row_stride = 0, long long head_stride = 0) {
+  for (int i = 0; i < kTmapHeights; ++i) {
+    const int rc = make_tmap(&set->m[i], base, dt, elem_bytes, rows, heads, head_dim, box_cols, kTmapRows[i], true, row_stride,
+                             head_stride);
+    if (rc != GDPA_OK) return rc;
+  }
+  return GDPA_OK;
+}
+
 // A wait that nothing satisfies: one thread waits on an mbarrier nobody arrives on, with a short
 // limit, so that the give-up path of the kernels' bounded waits (status word written, normal return)
 // can be exercised without hanging or faulting the GPU.
@@ -107,8 +118,8 @@ int check_common(const P* p) {
   if (p->head_dim != 64 && p->head_dim != 128) return GDPA_ERR_UNSUPPORTED_DIM;
   if (p->q_offsets == nullptr || p->kv_offsets == nullptr) return GDPA_ERR_BAD_ARG;
   if ((p->offsets_are_int64 & ~(GDPA_OFFSETS_INT64 | GDPA_OFFSETS_PAIRS)) != 0) return GDPA_ERR_BAD_ARG;
-  // TMA coordinates are 32-bit row indices.
-  if (p->total_q >= (1ll << 31) || p->total_kv >= (1ll << 31)) return GDPA_ERR_BAD_ARG;
+  // TMA coordinates are 32-bit row indices (the padding of a ragged tile is fetched from up to 127 rows past the end).
+  if (p->total_q >= (1ll << 31) - 128 || p->total_kv >= (1ll << 31) - 128) return GDPA_ERR_BAD_ARG;
   return GDPA_OK;
 }
 
@@ -243,15 +254,15 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   const void* vp = p->total_kv > 0 ? p->v : p->q;
   const long long kv_rows = p->total_kv > 0 ? p->total_kv : p->total_q;
   const bool no_kv = p->total_kv == 0;
-  if ((rc = make_tmap(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, kTile, true, p->q_strides[0],
-                      p->q_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_q, p->q, dt, eb, p->total_q, p->heads, p->head_dim, box_cols, p->q_strides[0],
+                          p->q_strides[1])) != GDPA_OK)
     return rc;
   const int kvh_map = p->total_kv > 0 ? kv_heads : p->heads;
-  if ((rc = make_tmap(&l.tm_k, kp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true,
-                      no_kv ? p->q_strides[0] : p->k_strides[0], no_kv ? p->q_strides[1] : p->k_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_k, kp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols,
+                          no_kv ? p->q_strides[0] : p->k_strides[0], no_kv ? p->q_strides[1] : p->k_strides[1])) != GDPA_OK)
     return rc;
-  if ((rc = make_tmap(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols, kTile, true,
-                      no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols,
+                          no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
     return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;
@@ -472,20 +483,18 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   BwdLaunch l;
   std::memset(&l, 0, sizeof(l));
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if ((rc = make_tmap(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true, p->q_strides[0],
-                      p->q_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_q, p->q, dt, 2, p->total_q, p->heads, p->head_dim, 64, p->q_strides[0], p->q_strides[1])) != GDPA_OK)
     return rc;
-  if ((rc = make_tmap(&l.tm_k, p->k, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true, p->k_strides[0],
-                      p->k_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_k, p->k, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, p->k_strides[0], p->k_strides[1])) != GDPA_OK)
     return rc;
-  if ((rc = make_tmap(&l.tm_v, p->v, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, kTile, true, p->v_strides[0],
-                      p->v_strides[1])) != GDPA_OK)
+  if ((rc = make_tmap_set(&l.tm_v, p->v, dt, 2, p->total_kv, kv_heads, p->head_dim, 64, p->v_strides[0], p->v_strides[1])) != GDPA_OK)
     return rc;
-  if ((rc = make_tmap(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64, kTile, true)) != GDPA_OK) return rc;
+  if ((rc = make_tmap_set(&l.tm_do, p->d_o, dt, 2, p->total_q, p->heads, p->head_dim, 64)) != GDPA_OK) return rc;
   // fp32 dQ accumulator, reduced into by 32-column x 32-row boxes (128-byte swizzled staging).
-  if ((rc = make_tmap(&l.tm_dq, p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
-                      32, true)) != GDPA_OK)
-    return rc;
+  for (int i = 0; i < kDqTmapHeights; ++i)
+    if ((rc = make_tmap(&l.tm_dq.m[i], p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
+                        32 >> i, true)) != GDPA_OK)
+      return rc;
   l.args.dk = static_cast<__nv_bfloat16*>(p->dk);
   l.args.dv = static_cast<__nv_bfloat16*>(p->dv);
   l.args.dq_accum = static_cast<float*>(p->dq_accum);

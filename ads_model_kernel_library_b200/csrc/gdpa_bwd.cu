@@ -19,9 +19,8 @@
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
 // dQ tiles are drained by a dedicated warpgroup (whole tile into registers, TMEM released, then each
 // warp stages its 32 rows in shared memory) and added into an fp32 accumulator by TMA reduce-add; a
-// second kernel rounds the accumulator to bf16.  Q rows of a tile beyond the sequence are forced to zero before they are
-// staged, so what the reduce adds to the rows of the next sequence is exactly zero; rows beyond the tensor are clipped by
-// the TMA unit.
+// second kernel rounds the accumulator to bf16.  Q rows of a ragged tile beyond the sequence are not touched: the reduce
+// of such a tile covers exactly the rows of the sequence (smaller boxes).
 //
 // Softmax: P^T = 2^(c S^T - lse[q]) from the forward's log-sum-exp and dS = scale P (dP - dPsum[q]); the
 // per-column statistics of a Q tile reach the element-wise warps through shared memory.
@@ -31,17 +30,13 @@
 // P^T of column half h is written over the first 32 columns of that half's own S^T columns
 // ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
-// Masking is by zero: score entries whose KV row or Q column lies beyond the sequence are zeroed
-// both in act(S) and in act'(S) (act'(0) is not 0 for GELU / SiLU), and dP there is replaced by zero before
-// it is multiplied, so rows of other sequences that a tile overlaps contribute exactly zero whatever they
-// hold (the reference's per-sequence block loads read them as zero,
-// gdpa/triton/triton_generalized_dot_product_attention.py:1575-1600).  The contractions always cover whole tiles, so
-// on a ragged tile the rows of Q, dO (last Q tile of a sequence) and K (last KV tile) beyond the sequence are
-// zero-filled in shared memory by the element-wise warps before they hand the tile's P^T to the MMA thread, i.e.
-// before dV, dK and dQ read those rows as the contraction dimension (0 x Inf would not be zero); S^T and dP^T, which
-// read them earlier, only get columns / rows from them that the selects above discard.
-#include <type_traits>
-
+// Tiles are loaded zero-padded (load_box_zero_padded): rows of a Q, dO, K or V tile beyond the end of its sequence
+// are zeros, not the next sequence's tokens, as with the reference's per-sequence block loads
+// (gdpa/triton/triton_generalized_dot_product_attention.py:1575-1600).  Score entries outside the sequence are
+// therefore S = 0, P = act(0) = 0 and dS = act'(0) x dP with dP = 0: exact zeros with no masking anywhere, and nothing
+// a neighbouring sequence holds (Inf and NaN included) reaches this one.  (Softmax: P = 2^(0 - lse) is not zero there,
+// but every product it enters has a zero partner: the padded dO, K and V rows and the zero dPsum.)  Only the band
+// (window_size) tests columns.
 #include "gdpa_common.cuh"
 #include "gdpa_launch.h"
 
@@ -122,9 +117,9 @@ struct BwdSmem {
 // ACC: dK / dV tiles are added into fp32 accumulators instead of stored (K / V rows shared between sequences).
 template <int D, int ACT, bool ACC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
+gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ TmapSet tm_k,
+                const __grid_constant__ TmapSet tm_v, const __grid_constant__ TmapSet tm_do,
+                const __grid_constant__ DqTmapSet tm_dq, const BwdArgs a) {
   using L = BwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -152,11 +147,11 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_relinquish();
   }
   if (warp == kBwdLoadWarp && lane == 0) {
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-    tma_prefetch_desc(&tm_do);
-    tma_prefetch_desc(&tm_dq);
+    tma_prefetch_desc(&tm_q.m[0]);
+    tma_prefetch_desc(&tm_k.m[0]);
+    tma_prefetch_desc(&tm_v.m[0]);
+    tma_prefetch_desc(&tm_do.m[0]);
+    tma_prefetch_desc(&tm_dq.m[0]);
   }
   tc_fence_before();
   __syncthreads();
@@ -191,36 +186,73 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const int q_row = static_cast<int>(w.q_start);
           GDPA_WAIT(BB_KV_EMPTY, kv_phase ^ 1u, ST_ROLE_LOAD);
           kv_phase ^= 1u;
+          const int kv_valid = w.lkv - w.blk * kTile;  // rows of this KV tile that belong to the sequence
           {
             const uint32_t bar = bar_base + 8u * BB_KV_FULL;
             mbar_arrive_expect_tx(bar, 2 * L::kTileBytes);
+            if (kv_valid >= kTile) {
 #pragma unroll
-            for (int hf = 0; hf < D / 64; ++hf)
-              tma_load_3d(smem_base + L::kKOff + hf * L::kHalfBytes, &tm_k, bar, hf * 64, w.h, kv_row);
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kKOff + hf * L::kHalfBytes, &tm_k.m[0], bar, hf * 64, w.h, kv_row);
 #pragma unroll
-            for (int hf = 0; hf < D / 64; ++hf)
-              tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v, bar, hf * 64, w.h, kv_row);
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v.m[0], bar, hf * 64, w.h, kv_row);
+            } else {
+              // a ragged tile: the boxes of K, then of V, zero-padded (one rolled loop: rare, and kept small)
+#pragma unroll 1
+              for (int i = 0; i < 2 * (D / 64); ++i) {
+                const bool is_v = i >= D / 64;
+                const int hf = is_v ? i - D / 64 : i;
+                load_box_zero_padded(smem_base + (is_v ? L::kVOff : L::kKOff) + hf * L::kHalfBytes, is_v ? tm_v : tm_k, bar,
+                                     hf * 64, w.h, kv_row, kv_valid, static_cast<int>(a.total_kv));
+              }
+            }
           }
           for (int m = 0; m < nq; ++m) {
             const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
-            GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
-            q_phase ^= 1u << st;
-            {
-              const uint32_t bar = bar_base + 8u * (BB_Q_FULL + st);
-              mbar_arrive_expect_tx(bar, L::kTileBytes);
+            const int q_valid = w.lq - mm * kTile;  // rows of this Q / dO tile that belong to the sequence
+            if (q_valid >= kTile) {
+              // a full tile: straight-line code, nothing between a buffer becoming free and its copies being issued
+              GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
+              q_phase ^= 1u << st;
+              {
+                const uint32_t bar = bar_base + 8u * (BB_Q_FULL + st);
+                mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-              for (int hf = 0; hf < D / 64; ++hf)
-                tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * 64, hq,
-                            q_row + mm * kTile);
-            }
-            GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
-            do_phase ^= 1u;
-            {
-              const uint32_t bar = bar_base + 8u * BB_DO_FULL;
-              mbar_arrive_expect_tx(bar, L::kTileBytes);
+                for (int hf = 0; hf < D / 64; ++hf)
+                  tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q.m[0], bar, hf * 64, hq,
+                              q_row + mm * kTile);
+              }
+              GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
+              do_phase ^= 1u;
+              {
+                const uint32_t bar = bar_base + 8u * BB_DO_FULL;
+                mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-              for (int hf = 0; hf < D / 64; ++hf)
-                tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do, bar, hf * 64, hq, q_row + mm * kTile);
+                for (int hf = 0; hf < D / 64; ++hf)
+                  tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do.m[0], bar, hf * 64, hq, q_row + mm * kTile);
+              }
+            } else {
+              // a ragged tile: the Q tile, then the dO tile, zero-padded (one rolled loop: rare, and kept small)
+#pragma unroll 1
+              for (int which = 0; which < 2; ++which) {
+                uint32_t bar;
+                if (which == 0) {
+                  GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
+                  q_phase ^= 1u << st;
+                  bar = bar_base + 8u * (BB_Q_FULL + st);
+                } else {
+                  GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
+                  do_phase ^= 1u;
+                  bar = bar_base + 8u * BB_DO_FULL;
+                }
+                mbar_arrive_expect_tx(bar, L::kTileBytes);
+                const uint32_t dst = smem_base + (which == 0 ? L::kQOff + st * L::kTileBytes : L::kDoOff);
+#pragma unroll 1
+                for (int hf = 0; hf < D / 64; ++hf)
+                  load_box_zero_padded(dst + hf * L::kHalfBytes, which == 0 ? tm_q : tm_do, bar, hf * 64, hq, q_row + mm * kTile,
+                                       q_valid, static_cast<int>(a.total_q));
+              }
             }
             st ^= 1u;
           }
@@ -339,13 +371,6 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float scale = a.scale, hscale = 0.5f * a.scale;
     uint8_t* sds_row = smem + L::kDsOff + half * L::kHalfBytes + row * 128;
     uint32_t s_phase = 0, dp_phase = 0, dkv_phase = 0, st_phase = 0;
-    // rows [lo, hi) of every 128-byte-row box of a tile, by the 256 element-wise threads
-    auto zero_rows = [&](uint8_t* tile, int lo, int hi) {
-#pragma unroll
-      for (int hf = 0; hf < D / 64; ++hf)
-        for (int off = lo * 128 + (threadIdx.x - 128) * 16; off < hi * 128; off += 256 * 16)
-          *reinterpret_cast<uint4*>(tile + hf * L::kHalfBytes + off) = make_uint4(0, 0, 0, 0);
-    };
     int tr = 0;
     const bool tracer = (threadIdx.x == 128);
     constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
@@ -376,16 +401,16 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       for (int m = 0; m < nq; ++m) {
         const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
-        // columns [clo, chi) of the tile take part for this thread's KV row: inside the Q length, the KV
-        // row inside the KV length, and inside the band
+        // Without a band nothing is masked: the tiles are zero-padded, so score entries outside the sequence are
+        // act(0) = 0 and their dS is act'(0) x 0 = 0.  With a band, columns [clo, chi) of the tile take part for this
+        // thread's KV row, and the unmasked path is taken by the warp as a whole.
         int clo = 0, chi = row_valid ? min(kTile, w.lq - mm * kTile) : 0;
+        bool full = true;
         if (a.window >= 0) {
           clo = max(clo, kv_local - a.window - mm * kTile);
           chi = min(chi, kv_local + a.window - mm * kTile + 1);
+          full = __all_sync(0xffffffffu, clo <= 0 && chi >= kTile);
         }
-        // the unmasked path is taken by the warp as a whole; without a band the test needs no vote
-        const bool full = (a.window < 0) ? ((w.blk + 1) * kTile <= w.lkv && w.lq - mm * kTile >= kTile)
-                                         : __all_sync(0xffffffffu, clo <= 0 && chi >= kTile);
         uint64_t g2[32];  // act'(S) * scale of this thread's 64 columns, as packed pairs
         uint32_t ra[32], rb[32];
         if (tracer) GDPA_TRACE(a, tr * 32 + 8);
@@ -421,8 +446,7 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (c == 0) tmem_ld32(tS + half * 64 + 32, rb);
           if constexpr (kSoftmax) {
             // P^T = 2^(c S^T - lse[q]) (already normalised); kept in g2 for dS = scale P (dP - dPsum)
-            // the column test in three instantiations: none on full tiles, the warp-uniform bound on edge tiles
-            // without a band, the per-thread range with a band
+            // the column test in two instantiations: none, or the per-thread range of a band
             auto emit = [&](auto inside) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
@@ -436,28 +460,13 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 g2[c * 16 + i] = pack_f32x2(p0, p1);
               }
             };
-            if (full) {
-              emit([](int) { return true; });
-            } else if (a.window < 0) {
-              const int qv = min(kTile, w.lq - mm * kTile);
-              emit([&](int col) { return row_valid && col < qv; });
-            } else {
-              emit([&](int col) { return col >= clo && col < chi; });
-            }
+            if (full) emit([](int) { return true; });
+            else emit([&](int col) { return col >= clo && col < chi; });
           } else if (full) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               act_and_grad_pair<ACT, false>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
                                             true, true, pk[i], g2[c * 16 + i]);
-          } else if (a.window < 0) {
-            // edge tile without a band: the column bound is the same for every thread (cheap predicates)
-            const int qv = min(kTile, w.lq - mm * kTile);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = half * 64 + c * 32 + 2 * i;
-              act_and_grad_pair<ACT, true>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale,
-                                           row_valid && (col < qv), row_valid && (col + 1 < qv), pk[i], g2[c * 16 + i]);
-            }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -470,21 +479,6 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st16(tS + half * 64 + c * 16, pk);
         }
         tmem_wait_st();
-        // (a test on the tile's geometry alone, the same for all 256 threads: with a band `full` differs between warps)
-        if ((a.window < 0) ? !full : ((w.blk + 1) * kTile > w.lkv || w.lq - mm * kTile < kTile)) {
-          // A ragged tile (rare: the last Q tile of a sequence, or every tile of its last KV tile).  The rows of Q, dO
-          // and K beyond the sequence belong to the next one; dV, dK and dQ contract over them against zeros, and
-          // 0 x Inf is not zero: clear them before the MMA thread is allowed to go on.  dp_phase has not been flipped
-          // for this tile yet, so it is the parity of the dO barrier and the stage of the Q tile (all flip per tile).
-          const int q_valid = w.lq - mm * kTile;
-          if (q_valid < kTile) {
-            GDPA_WAIT_WARP(BB_DO_FULL, dp_phase, ST_ROLE_ACT);  // the dO tile has landed
-            zero_rows(smem + L::kDoOff, q_valid, kTile);
-            zero_rows(smem + L::kQOff + dp_phase * L::kTileBytes, q_valid, kTile);
-          }
-          if (m == 0 && w.lkv - w.blk * kTile < kTile) zero_rows(smem + L::kKOff, w.lkv - w.blk * kTile, kTile);
-          fence_proxy_async_smem();
-        }
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_P_FULL);
         if (tracer) GDPA_TRACE(a, tr * 32 + 10);
@@ -493,65 +487,44 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         dp_phase ^= 1u;
         tc_fence_after();
         if (tracer) GDPA_TRACE(a, tr * 32 + 11);
-        // dS^T = act'(S^T) * dP^T for this thread's 64 columns.  Two instantiations, chosen per tile: the common one has
-        // no test per element; on a ragged tile dP outside the sequence (rows and columns that come from other
-        // sequences' tokens) is replaced by zero, so that the product with act' = 0 is zero whatever it held.  (A
-        // separate instantiation rather than a fix-up of the loaded registers inside a branch: merging such a branch
-        // back costs a register move per value on the common path.)
-        auto ds_phase = [&](auto masked_tag) {
-          constexpr bool kMasked = decltype(masked_tag)::value;
-          int lo = 0, hi = kTile;
-          if constexpr (kMasked) {
-            hi = row_valid ? min(kTile, w.lq - mm * kTile) : 0;
-            if (a.window >= 0) {
-              lo = max(lo, kv_local - a.window - mm * kTile);
-              hi = min(hi, kv_local + a.window - mm * kTile + 1);
-            }
-          }
-          tmem_ld32(tDP + half * 64, ra);
+        // dS^T = act'(S^T) * dP^T for this thread's 64 columns (dP^T is finite everywhere: the operands are zero-padded)
+        tmem_ld32(tDP + half * 64, ra);
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t(&cur)[32] = c ? rb : ra;
-            tmem_wait_ld();
-            tmem_regs_ready(cur);
-            if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
-            uint32_t pk[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t(&cur)[32] = c ? rb : ra;
+          tmem_wait_ld();
+          tmem_regs_ready(cur);
+          if (c == 0) tmem_ld32(tDP + half * 64 + 32, rb);
+          uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t d[4];
+          for (int j = 0; j < 4; ++j) {
+            uint32_t d[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float x0 = __uint_as_float(cur[8 * j + 2 * e]), x1 = __uint_as_float(cur[8 * j + 2 * e + 1]);
-                if constexpr (kMasked) {
-                  const int col = half * 64 + c * 32 + 8 * j + 2 * e;
-                  x0 = (col >= lo && col < hi) ? x0 : 0.f;
-                  x1 = (col + 1 >= lo && col + 1 < hi) ? x1 : 0.f;
-                }
-                float d0, d1;
-                if constexpr (kSoftmax) {
-                  const float2 ps = *reinterpret_cast<const float2*>(stat_dps + (m & 1) * kTile + half * 64 + c * 32 + 8 * j + 2 * e);
-                  float p0, p1;
-                  unpack_f32x2(g2[c * 16 + 4 * j + e], p0, p1);
-                  d0 = p0 * (x0 - ps.x) * scale;
-                  d1 = p1 * (x1 - ps.y) * scale;
-                } else {
-                  unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e], pack_f32x2(x0, x1)), d0, d1);
-                }
-                d[e] = pack_bf16x2(d0, d1);
+            for (int e = 0; e < 4; ++e) {
+              float d0, d1;
+              if constexpr (kSoftmax) {
+                const float2 ps = *reinterpret_cast<const float2*>(stat_dps + (m & 1) * kTile + half * 64 + c * 32 + 8 * j + 2 * e);
+                float p0, p1;
+                unpack_f32x2(g2[c * 16 + 4 * j + e], p0, p1);
+                d0 = p0 * (__uint_as_float(cur[8 * j + 2 * e]) - ps.x) * scale;
+                d1 = p1 * (__uint_as_float(cur[8 * j + 2 * e + 1]) - ps.y) * scale;
+              } else {
+                unpack_f32x2(mul_f32x2(g2[c * 16 + 4 * j + e],
+                                       pack_f32x2(__uint_as_float(cur[8 * j + 2 * e]), __uint_as_float(cur[8 * j + 2 * e + 1]))),
+                             d0, d1);
               }
-              // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
-              *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
-              pk[4 * j + 0] = d[0];
-              pk[4 * j + 1] = d[1];
-              pk[4 * j + 2] = d[2];
-              pk[4 * j + 3] = d[3];
+              d[e] = pack_bf16x2(d0, d1);
             }
-            // the same values as the A operand of dK, over dP^T columns this half has already read
-            tmem_st16(tDP + half * 64 + c * 16, pk);
+            // 16-byte chunk (4c + j) of this row's 128-byte line, XOR-swizzled by the row index
+            *reinterpret_cast<uint4*>(sds_row + (((c * 4 + j) ^ (row & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
+            pk[4 * j + 0] = d[0];
+            pk[4 * j + 1] = d[1];
+            pk[4 * j + 2] = d[2];
+            pk[4 * j + 3] = d[3];
           }
-        };
-        if (full) ds_phase(std::false_type{});
-        else ds_phase(std::true_type{});
+          // the same values as the A operand of dK, over dP^T columns this half has already read
+          tmem_st16(tDP + half * 64 + c * 16, pk);
+        }
         tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before();
@@ -637,37 +610,40 @@ gdpa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         mbar_arrive(bar_base + 8u * BB_DQ_EMPTY);
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 15);
-        // Two instantiations of the staging loop, chosen per tile.  Rows of a ragged tile beyond the sequence belong to
-        // the next one: their dS is zero, but a zero times a non-finite K row of THIS sequence is not, so what would be
-        // added to those rows is forced to zero (rare path; a fix-up of the registers inside a branch would cost a move
-        // per value on the common path).
-        auto stage_and_reduce = [&](auto masked_tag) {
-          constexpr bool kMasked = decltype(masked_tag)::value;
-          uint32_t keep = 0xffffffffu;
-          if constexpr (kMasked) keep = (mm * kTile + warp * 32 + lane < w.lq) ? 0xffffffffu : 0u;
+        // Rows of a ragged tile beyond the sequence belong to the next one and must not be touched (their dS is zero, but
+        // a zero times a non-finite K row of THIS sequence is not): the reduce-add of a slab with fewer than 32 rows of
+        // the sequence is issued as boxes of 16, 8, 4, 2, 1 rows that cover exactly those rows.
+        const int slab_rows = w.lq - mm * kTile - warp * 32;
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            const uint32_t buf = slab & 1u;
-            // the reduce that read this staging buffer two slabs ago must have finished reading it
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
+        for (int c = 0; c < D / 32; ++c) {
+          const uint32_t buf = slab & 1u;
+          // the reduce that read this staging buffer two slabs ago must have finished reading it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              uint4 v = make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
-              if constexpr (kMasked) v = make_uint4(v.x & keep, v.y & keep, v.z & keep, v.w & keep);
-              *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) = v;
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(stage_row + buf * kDqWarpSlabBytes + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(r[c][4 * j], r[c][4 * j + 1], r[c][4 * j + 2], r[c][4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (slab_rows >= 32) {
+              tma_reduce_add_3d(&tm_dq.m[0], stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
+            } else {
+              int done = 0;
+#pragma unroll 1
+              for (int k = 1; k < kDqTmapHeights; ++k) {
+                const int h = 32 >> k;
+                if (slab_rows - done >= h) {
+                  tma_reduce_add_3d(&tm_dq.m[k], stage_base + buf * kDqWarpSlabBytes + done * 128, c * 32, hq, q_row0 + done);
+                  done += h;
+                }
+              }
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_3d(&tm_dq, stage_base + buf * kDqWarpSlabBytes, c * 32, hq, q_row0);
-              tma_store_commit();
-            }
-            ++slab;
+            tma_store_commit();
           }
-        };
-        if (mm * kTile + warp * 32 + 32 > w.lq) stage_and_reduce(std::true_type{});
-        else stage_and_reduce(std::false_type{});
+          ++slab;
+        }
         if (threadIdx.x == 0) GDPA_TRACE(a, tr * 32 + 16);
         ++tr;
       }

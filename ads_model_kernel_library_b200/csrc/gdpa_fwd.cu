@@ -10,9 +10,7 @@
 //   warps 8-15  the same for Q tile 1
 //   warp  16    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
 //               O_s += P_s V (A operand P read from TMEM)
-//   warp  17    TMA loader (one lane)
-//   warp  18    tail fixer: zero-fills the V rows of a sequence's last, partly filled KV tile that the PV
-//               contraction still reads;  warp 19 idle
+//   warp  17    TMA loader (one lane);  warps 18-19 idle
 //
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).  P_s (bf16, two
 // values per column) of column half h overwrites the first 32 columns of that half's own S columns.
@@ -23,15 +21,12 @@
 // maxima through shared memory, keep partial row sums and write the log-sum-exp for the backward), and
 // FP8 e4m3 operands with per-128-token-block scales.
 //
-// Rows of a tile that lie beyond the end of a sequence hold other sequences' tokens (or zeros
-// past the end of the tensor).  Nothing of them reaches this sequence's output, whatever their values
-// (the reference's per-sequence block loads read such rows as zero,
-// gdpa/triton/triton_generalized_dot_product_attention.py:270, :317): on the last KV tile of a sequence
-// the MMAs cover only the valid rows rounded up to one K slice (S = Q K^T with N < 128, P V with fewer
-// K slices), S columns beyond the KV length are replaced (a select, not a multiplication) by zero before
-// the activation (act(0) = 0 for every supported activation), and the few V rows between the KV length and
-// the end of its K slice are zero-filled in shared memory before P V reads them, so that 0 x Inf never
-// occurs.  Q rows beyond the Q length are computed and never stored.
+// Tiles are loaded zero-padded (load_box_zero_padded): rows of a tile beyond the end of its sequence are zeros,
+// not the next sequence's tokens, as with the reference's per-sequence block loads
+// (gdpa/triton/triton_generalized_dot_product_attention.py:270, :317).  So S columns beyond the KV length are
+// exactly 0 and act(0) = 0 for every supported element-wise activation: no masking, and nothing a neighbouring
+// sequence holds (Inf and NaN included) reaches this one.  Only the softmax (where a padded column must not count)
+// and the band (window_size) test columns.  Q rows beyond the Q length are computed and never stored.
 #include "gdpa_common.cuh"
 #include "gdpa_launch.h"
 
@@ -58,20 +53,8 @@ enum FwdBar : int {
   B_O_EMPTY = 10 + 2 * kKvStages,      // [2] epilogue (128 arrivals) -> MMA
   B_L_FULL = 12 + 2 * kKvStages,       // [2] softmax: activation group -> epilogue (row sums)
   B_M_FULL = 14 + 2 * kKvStages,       // [2] softmax, wide layout: both column halves have published their row maxima
-  // [kKvStages / 2] tail fixer -> MMA: the rows past the sequence of the V tile in ring stage 2 i + 1 are zero.
-  // One barrier per V stage: a later arrival on the same barrier needs that stage refilled, hence released by the
-  // MMA thread after its wait, so the barrier can never run more than one phase ahead of the waiter.
-  B_V_FIXED = 16 + 2 * kKvStages,
-  B_COUNT = 16 + 2 * kKvStages + kKvStages / 2
+  B_COUNT = 16 + 2 * kKvStages
 };
-
-// Rows of a sequence's last KV tile the contractions read: the valid rows rounded up to one K slice of P V
-// (16 rows of bf16, 32 of e4m3).
-template <int EB>
-__device__ __forceinline__ int fwd_rows_used(int valid) {
-  constexpr int kRowsPerSlice = 32 / EB;
-  return (valid + kRowsPerSlice - 1) / kRowsPerSlice * kRowsPerSlice;
-}
 
 template <int D, int EB>
 struct FwdSmem {
@@ -117,14 +100,13 @@ __device__ __forceinline__ float sumsq_bf16x8(const uint4& v) {
 // rather than a run-time branch, so that the plain forward carries none of it.
 template <int D, int ACT, bool FP8, bool FUSE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
-gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
+gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ TmapSet tm_k,
+                const __grid_constant__ TmapSet tm_v, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
   constexpr int kActWarps = 16;
   constexpr int kMmaWarp = 16;
   constexpr int kLoadWarp = 17;
-  constexpr int kFixWarp = 18;
   constexpr uint32_t kStageThreads = 256u;  // threads that work on one Q tile's S / O
   using L = FwdSmem<D, EB>;
   extern __shared__ uint8_t smem_raw[];
@@ -146,8 +128,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if ((i >= B_P_FULL && i < B_P_FULL + 2) || (i >= B_O_EMPTY && i < B_O_EMPTY + 2) ||
           (i >= B_L_FULL && i < B_L_FULL + 2) || (i >= B_M_FULL && i < B_M_FULL + 2))
         cnt = kStageThreads;
-      // a V slot (odd ring stage) is released by the MMA thread's commit and by the tail fixer
-      if (i >= B_KV_EMPTY && i < B_KV_EMPTY + kKvStages && ((i - B_KV_EMPTY) & 1)) cnt = 2u;
       mbar_init(bar_base + 8u * i, cnt);
     }
     *abort_flag = 0;
@@ -158,9 +138,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_relinquish();
   }
   if (warp == kLoadWarp && lane == 0) {
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_q.m[0]);
+    tma_prefetch_desc(&tm_k.m[0]);
+    tma_prefetch_desc(&tm_v.m[0]);
   }
   tc_fence_before();
   __syncthreads();
@@ -172,7 +152,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // Operand format code: 1 = bf16 for kind::f16, 0 = e4m3 for kind::f8f6f4.
   constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   // QK: A = Q tile (K-major), B = K tile (K-major), M = 128, N = 128.
-  constexpr uint32_t kIdescQK0 = umma_idesc(kFmt, kFmt, 0, 0, kTile, 0);  // N goes in per MMA (bits 17-22)
+  constexpr uint32_t kIdescQK = umma_idesc(kFmt, kFmt, 0, 0, kTile, kTile);
   // PV: A = P in TMEM, B = V tile (MN-major: head dim contiguous), M = 128, N = D.
   constexpr uint32_t kIdescPV = umma_idesc(kFmt, kFmt, 0, 1, kTile, D);
 
@@ -201,21 +181,23 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             q_phase ^= 1u << s;
             const uint32_t bar = bar_base + 8u * (B_Q_FULL + s);
             mbar_arrive_expect_tx(bar, L::kTileBytes);
-#pragma unroll
+            const int valid = w.lq - q0 - s * kTile;  // rows of this Q tile that belong to the sequence
+#pragma unroll 1
             for (int hf = 0; hf < L::kBoxes; ++hf)
-              tma_load_3d(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, &tm_q, bar, hf * L::kBoxCols,
-                          w.h, q_row + s * kTile);
+              load_box_zero_padded(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, tm_q, bar,
+                                   hf * L::kBoxCols, w.h, q_row + s * kTile, valid, static_cast<int>(a.total_q));
           } else {
             const int t = (step == 1) ? 0 : step - 2;  // 0 = K0, 1 = V0, 2 = K1, ...
             const int j = t >> 1;
-            const CUtensorMap* tm = (t & 1) ? &tm_v : &tm_k;
+            const TmapSet& tm = (t & 1) ? tm_v : tm_k;
             GDPA_WAIT(B_KV_EMPTY + kv_stage, kv_phase ^ 1u, ST_ROLE_LOAD);
             const uint32_t bar = bar_base + 8u * (B_KV_FULL + kv_stage);
             mbar_arrive_expect_tx(bar, L::kTileBytes);
-#pragma unroll
+            const int valid = w.lkv - (j0 + j) * kTile;  // rows of this KV tile that belong to the sequence
+#pragma unroll 1
             for (int hf = 0; hf < L::kBoxes; ++hf)
-              tma_load_3d(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar,
-                          hf * L::kBoxCols, w.h / a.kv_group, kv_row + j * kTile);
+              load_box_zero_padded(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar,
+                                   hf * L::kBoxCols, w.h / a.kv_group, kv_row + j * kTile, valid, static_cast<int>(a.total_kv));
             if (++kv_stage == kKvStages) {
               kv_stage = 0;
               kv_phase ^= 1u;
@@ -229,18 +211,16 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) {
       uint32_t kv_stage = 0, kv_phase = 0;
       // bit s of q_phase / p_phase / o_phase = parity of that barrier of Q tile s (registers, not arrays indexed by s)
-      uint32_t q_phase = 0, p_phase = 0, o_phase = 0, vfix_phase = 0;
+      uint32_t q_phase = 0, p_phase = 0, o_phase = 0;
       int tr = 0;
       // Descriptors of stage 0 / ring slot 0, built once; per MMA only the low word moves.
       const uint64_t dq0 = umma_smem_desc_sw128(smem_base + L::kQOff, 16, 1024);
       const uint64_t dk0 = umma_smem_desc_sw128(smem_base + L::kKvOff, 16, 1024);
       const uint64_t dv0 = umma_smem_desc_sw128(smem_base + L::kKvOff, L::kHalfBytes, 1024);
-      // `n` = KV rows of the tile the contraction covers (a multiple of 16; fewer than 128 only on the last tile)
-      auto issue_qk = [&](int s, uint32_t k_stage, int n) {
+      auto issue_qk = [&](int s, uint32_t k_stage) {
         const uint64_t da = umma_desc_advance(dq0, s * L::kTileBytes);
         const uint64_t db = umma_desc_advance(dk0, k_stage * L::kTileBytes);
         const uint32_t d_tmem = tmem_base + s * kTile;
-        const uint32_t kIdescQK = kIdescQK0 | (static_cast<uint32_t>(n >> 3) << 17);
         // one K slice = 32 bytes of the head dim (16 bf16 or 32 e4m3), four slices per 128-byte box
 #pragma unroll
         for (int kk = 0; kk < D * EB / 32; ++kk) {
@@ -249,26 +229,18 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           else umma_ss_f16(d_tmem, umma_desc_advance(da, off), umma_desc_advance(db, off), kIdescQK, kk > 0 ? 1u : 0u);
         }
       };
-      // `nsl` = K slices (16 or 32 KV rows each) that hold rows of the sequence.  A full tile takes the unrolled loop
-      // without a test per MMA; only a sequence's ragged last tile takes the counted loop.
-      constexpr int kRowsPerSlice = 32 / EB;
-      constexpr int kSlices = kTile / kRowsPerSlice;
-      auto issue_pv = [&](int s, uint32_t v_stage, bool accumulate, int nsl) {
+      auto issue_pv = [&](int s, uint32_t v_stage, bool accumulate) {
         const uint64_t db = umma_desc_advance(dv0, v_stage * L::kTileBytes);
         const uint32_t d_tmem = tmem_base + 256 + s * kTile, a_tmem = tmem_base + s * kTile;
-        // one K slice = 16 (bf16) or 32 (e4m3) KV rows of 128 bytes; P holds it in 8 TMEM columns; the P slices of
-        // column half h sit at the start of that half's own S columns
-        auto one = [&](int kk) {
+        // one K slice = 16 (bf16) or 32 (e4m3) KV rows of 128 bytes; P holds it in 8 TMEM columns
+        constexpr int kRowsPerSlice = 32 / EB;
+#pragma unroll
+        for (int kk = 0; kk < kTile / kRowsPerSlice; ++kk) {
           const uint32_t acc = (accumulate || kk > 0) ? 1u : 0u;
+          // the P slices of column half h sit at the start of that half's own S columns
           const uint32_t a_col = FP8 ? (kk >> 1) * 64 + (kk & 1) * 8 : (kk >> 2) * 64 + (kk & 3) * 8;
           if constexpr (FP8) umma_ts_f8(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
           else umma_ts_f16(d_tmem, a_tmem + a_col, umma_desc_advance(db, kk * kRowsPerSlice * 128), kIdescPV, acc);
-        };
-        if (nsl == kSlices) {
-#pragma unroll
-          for (int kk = 0; kk < kSlices; ++kk) one(kk);
-        } else {
-          for (int kk = 0; kk < nsl; ++kk) one(kk);
         }
       };
       WorkWalker walker(n_items);
@@ -279,10 +251,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         fwd_kv_range(w, a.window, j0, nkv);
         if (nkv == 0) continue;
         const int nst = (w.lq - w.blk * kFwdQBlock > kTile) ? 2 : 1;
-        // the last KV tile the item visits: rows of the sequence in it, rows the MMAs cover
-        const int last_valid = min(kTile, w.lkv - (j0 + nkv - 1) * kTile);
-        const int last_used = fwd_rows_used<EB>(last_valid);
-        const int last_n = (last_valid + 15) & ~15;
         // First S tiles: S_s = Q_s K_0^T.
         {
           const uint32_t k_stage = kv_stage;
@@ -291,7 +259,7 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             q_phase ^= 1u << s;
             if (s == 0) GDPA_WAIT(B_KV_FULL + k_stage, kv_phase, ST_ROLE_MMA);
             tc_fence_after();
-            issue_qk(s, k_stage, nkv == 1 ? last_n : kTile);
+            issue_qk(s, k_stage);
             tc_commit(bar_base + 8u * (B_S_FULL + s));
             if (nkv == 1) tc_commit(bar_base + 8u * (B_Q_EMPTY + s));
           }
@@ -305,12 +273,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const uint32_t k_stage = kv_stage, k_phase = kv_phase;  // K_{j+1}, valid if more
           if (more) { if (++kv_stage == kKvStages) { kv_stage = 0; kv_phase ^= 1u; } }
           GDPA_WAIT(B_KV_FULL + v_stage, v_phase, ST_ROLE_MMA);
-          if (!more && last_used != last_valid) {
-            // the V rows between the end of the sequence and the end of its K slice have been zero-filled
-            GDPA_WAIT(B_V_FIXED + (v_stage >> 1), (vfix_phase >> (v_stage >> 1)) & 1u, ST_ROLE_MMA);
-            vfix_phase ^= 1u << (v_stage >> 1);
-          }
-          const int v_slices = more ? kSlices : last_used / kRowsPerSlice;
           for (int s = 0; s < nst; ++s) {
             GDPA_TRACE(a, tr * 32 + 16 + s * 4 + 0);
             GDPA_WAIT(B_P_FULL + s, (p_phase >> s) & 1u, ST_ROLE_MMA);
@@ -321,13 +283,13 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               o_phase ^= 1u << s;
             }
             tc_fence_after();
-            issue_pv(s, v_stage, j > 0, v_slices);
+            issue_pv(s, v_stage, j > 0);
             if (more) {
               if (s == 0) {
                 GDPA_WAIT(B_KV_FULL + k_stage, k_phase, ST_ROLE_MMA);
                 tc_fence_after();
               }
-              issue_qk(s, k_stage, j + 2 == nkv ? last_n : kTile);
+              issue_qk(s, k_stage);
               tc_commit(bar_base + 8u * (B_S_FULL + s));
               if (j + 2 == nkv) tc_commit(bar_base + 8u * (B_Q_EMPTY + s));
             } else {
@@ -338,46 +300,6 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ++tr;
           tc_commit(bar_base + 8u * (B_KV_EMPTY + v_stage));
           if (more) tc_commit(bar_base + 8u * (B_KV_EMPTY + k_stage));
-        }
-      }
-    }
-   } else if (warp == kFixWarp) {
-    // ------------------------------------------------------------------ tail fixer
-    // The P V contraction of a sequence's last KV tile reads whole K slices; the V rows of the last slice that
-    // lie beyond the sequence belong to the next sequence (P is zero there, but 0 x Inf is not).  This warp
-    // zero-fills those rows once the tile has landed.  It is a second consumer of every V slot of the ring
-    // (the odd stages: slots alternate K, V and every item uses an even number of them): it waits for each V
-    // tile and releases it, so it can neither run ahead of the loader nor be lapped by it.
-    static_assert(kKvStages % 2 == 0, "V tiles must always land in the same (odd) stages");
-    uint32_t kv_stage = 1, kv_phase = 0;
-    WorkWalker walker(n_items);
-    int idx;
-    while (walker.next(idx)) {
-      const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim, a.kv_index);
-      int j0, nkv;
-      fwd_kv_range(w, a.window, j0, nkv);
-      if (nkv == 0) continue;
-      const int valid = min(kTile, w.lkv - (j0 + nkv - 1) * kTile);
-      const int used = fwd_rows_used<EB>(valid);
-      for (int j = 0; j < nkv; ++j) {
-        GDPA_WAIT_WARP(B_KV_FULL + kv_stage, kv_phase, ST_ROLE_FIX);
-        if (j == nkv - 1 && used != valid) {
-          // a row of a box is 128 contiguous bytes (the swizzle permutes inside a row), rows are consecutive
-#pragma unroll
-          for (int hf = 0; hf < L::kBoxes; ++hf) {
-            uint8_t* box = smem + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes;
-            for (int off = valid * 128 + lane * 16; off < used * 128; off += 32 * 16)
-              *reinterpret_cast<uint4*>(box + off) = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_base + 8u * (B_V_FIXED + (kv_stage >> 1)));
-        }
-        if (lane == 0) mbar_arrive(bar_base + 8u * (B_KV_EMPTY + kv_stage));
-        kv_stage += 2;
-        if (kv_stage >= kKvStages) {
-          kv_stage = 1;
-          kv_phase ^= 1u;
         }
       }
     }
@@ -638,8 +560,9 @@ gdpa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_st8(s_tmem + c * 8, p8);
             continue;
           }
-          // the unmasked path is taken by the warp as a whole
-          if (__all_sync(0xffffffffu, clo <= c * 32 && chi >= (c + 1) * 32)) {
+          // without a band nothing is masked (the tile's padding is zero, act(0) = 0); with one, the unmasked path
+          // is taken by the warp as a whole
+          if (a.window < 0 || __all_sync(0xffffffffu, clo <= c * 32 && chi >= (c + 1) * 32)) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               pk[i] = act_scaled_pair_bf16<ACT>(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]), scale, hscale);

@@ -14,6 +14,21 @@ constexpr int GDPA_ERR_UNSUPPORTED_DIM_ = 2;
 constexpr int GDPA_ERR_UNSUPPORTED_ACT_ = 4;
 constexpr int GDPA_ERR_LAUNCH_ = 6;
 
+// The tensor maps of one tensor: boxes of 128, 64, 16, 4 and 1 rows (same box width), so that a tile with fewer
+// than 128 valid rows can be fetched as a few boxes that cover exactly those rows.
+constexpr int kTmapHeights = 5;
+constexpr int kTmapRows[kTmapHeights] = {128, 64, 16, 4, 1};
+struct TmapSet {
+  CUtensorMap m[kTmapHeights];
+};
+
+// The maps of the fp32 dQ accumulator: boxes of 32 columns x 32, 16, 8, 4, 2, 1 rows, so that the reduce-add of a
+// ragged tile covers exactly the rows of its sequence.
+constexpr int kDqTmapHeights = 6;
+struct DqTmapSet {
+  CUtensorMap m[kDqTmapHeights];
+};
+
 struct FwdArgs {
   __nv_bfloat16* o;
   const void* q_off;
@@ -104,7 +119,7 @@ struct NormBwdArgs {
 };
 
 struct FwdLaunch {
-  CUtensorMap tm_q, tm_k, tm_v;
+  TmapSet tm_q, tm_k, tm_v;
   FwdArgs args;
   int grid;
   cudaStream_t stream;
@@ -136,7 +151,8 @@ struct BwdArgs {
 };
 
 struct BwdLaunch {
-  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq;
+  TmapSet tm_q, tm_k, tm_v, tm_do;
+  DqTmapSet tm_dq;
   BwdArgs args;
   int grid;
   cudaStream_t stream;
