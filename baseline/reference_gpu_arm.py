@@ -25,7 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
 
 
-def worker(kind: str, L: int, B: int, mode: str, cell_ms: float) -> None:
+def worker(kind: str, lengths, B: int, mode: str, cell_ms: float) -> None:
+    """All lengths of one (set, pass) in one process, so that the kernels compile once."""
     import numpy as np
     import torch
 
@@ -35,63 +36,72 @@ def worker(kind: str, L: int, B: int, mode: str, cell_ms: float) -> None:
     torch.manual_seed(2025)
     H, D = 4, 128
     dev = torch.device("cuda", 0)
-    rng = np.random.default_rng(2025 + L)
-    lq = rng.integers(1, L + 1, B) if kind == "self_s05" else np.full(B, L)
-    dff = 256 if kind == "cross_kv256" else L
-    q_off = torch.from_numpy(np.concatenate([[0], np.cumsum(lq)])).to(torch.int32).to(dev)
-    kv_off = (torch.arange(B + 1, dtype=torch.int32) * dff).to(dev)
     grad = mode == "bwd"
-    q = torch.randn(int(lq.sum()), H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
-    k = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
-    v = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
-    tq = precompute_for_varline_load_balancing(q, q_off, kv_off)
-    kw = dict(q=q, k=k, v=v, cu_seqlens_q=q_off, cu_seqlens_k=kv_off, max_seqlen_q=int(lq.max()), max_seqlen_k=dff,
-              prefer_persistent=True, tile_to_batch_q=tq[0], tile_to_head_q=tq[1], tile_to_block_q=tq[2], activation="fast_gelu")
-    if grad:
-        tk = precompute_for_varline_load_balancing(q, q_off, kv_off, is_bwd=True)
-        kw.update(tile_to_batch_k=tk[0], tile_to_head_k=tk[1], tile_to_block_k=tk[2])
-    pairs = float((lq.astype(np.float64) * dff).sum())
-    flops = 4.0 * H * D * pairs * (2.5 if grad else 1.0)
-    if grad:
-        res = flash_attn_varlen_func(**kw)
-        out = res[0] if isinstance(res, (tuple, list)) else res
-        dout = torch.randn_like(out)
+    for L in lengths:
+        rng = np.random.default_rng(2025 + L)
+        lq = rng.integers(1, L + 1, B) if kind == "self_s05" else np.full(B, L)
+        dff = 256 if kind == "cross_kv256" else L
+        q_off = torch.from_numpy(np.concatenate([[0], np.cumsum(lq)])).to(torch.int32).to(dev)
+        kv_off = (torch.arange(B + 1, dtype=torch.int32) * dff).to(dev)
+        q = torch.randn(int(lq.sum()), H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+        k = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+        v = torch.randn(B * dff, H, D, dtype=torch.bfloat16, device=dev, requires_grad=grad)
+        tq = precompute_for_varline_load_balancing(q, q_off, kv_off)
+        kw = dict(q=q, k=k, v=v, cu_seqlens_q=q_off, cu_seqlens_k=kv_off, max_seqlen_q=int(lq.max()), max_seqlen_k=dff,
+                  prefer_persistent=True, tile_to_batch_q=tq[0], tile_to_head_q=tq[1], tile_to_block_q=tq[2], activation="fast_gelu")
+        if grad:
+            tk = precompute_for_varline_load_balancing(q, q_off, kv_off, is_bwd=True)
+            kw.update(tile_to_batch_k=tk[0], tile_to_head_k=tk[1], tile_to_block_k=tk[2])
+        pairs = float((lq.astype(np.float64) * dff).sum())
+        flops = 4.0 * H * D * pairs * (2.5 if grad else 1.0)
+        if grad:
+            res = flash_attn_varlen_func(**kw)
+            out = res[0] if isinstance(res, (tuple, list)) else res
+            dout = torch.randn_like(out)
 
-        def fn():
-            q.grad = k.grad = v.grad = None
-            out.backward(dout, retain_graph=True)
-    else:
-        def fn():
-            with torch.no_grad():
-                flash_attn_varlen_func(**kw)
-    for _ in range(3):
-        fn()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(); fn(); b.record(); torch.cuda.synchronize()
-    reps = int(min(200, max(5, cell_ms / max(a.elapsed_time(b), 1e-3))))
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-    for x, y in evs:
-        x.record(); fn(); y.record()
-    torch.cuda.synchronize()
-    ms = float(np.median([x.elapsed_time(y) for x, y in evs]))
-    print("RESULT " + json.dumps({"impl": "reference_kernel", "metric": f"gdpa_{mode}_useful_tflops", "value": flops / (ms * 1e-3) / 1e12,
-                                  "unit": "TFLOP/s", "ms_per_step": ms, "steps": reps,
-                                  "config": {"workload": f"ref_{kind}_{mode}_L{L}", "batch": B, "heads": H, "head_dim": D,
-                                             "activation": "fast_gelu", "api": "flash_attn_varlen_func (CuteDSL, persistent)"}}), flush=True)
+            def fn():
+                q.grad = k.grad = v.grad = None
+                out.backward(dout, retain_graph=True)
+        else:
+            def fn():
+                with torch.no_grad():
+                    flash_attn_varlen_func(**kw)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record(); torch.cuda.synchronize()
+        reps = int(min(200, max(5, cell_ms / max(a.elapsed_time(b), 1e-3))))
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for x, y in evs:
+            x.record(); fn(); y.record()
+        torch.cuda.synchronize()
+        ms = float(np.median([x.elapsed_time(y) for x, y in evs]))
+        print("RESULT " + json.dumps({"impl": "reference_kernel", "metric": f"gdpa_{mode}_useful_tflops",
+                                      "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": reps,
+                                      "config": {"workload": f"ref_{kind}_{mode}_L{L}", "batch": B, "heads": H, "head_dim": D,
+                                                 "activation": "fast_gelu", "api": "flash_attn_varlen_func (CuteDSL, persistent)"}}),
+              flush=True)
+        del q, k, v
+        torch.cuda.empty_cache()
 
 
-def run_cell(kind, L, B, mode, cell_ms, limit_s):
-    cmd = [sys.executable, os.path.abspath(__file__), "--worker", kind, str(L), str(B), mode, str(cell_ms)]
+def run_cells(kind, lengths, B, mode, cell_ms, limit_s):
+    """Results of the cells that finished, and an error text if the child failed or ran out of time."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--worker", kind, ",".join(str(x) for x in lengths), str(B), mode, str(cell_ms)]
+    err = None
     try:
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=limit_s)
-    except subprocess.TimeoutExpired:
-        return None, f"no result within {limit_s} s (compile or kernel did not finish)"
-    for line in r.stdout.splitlines():
-        if line.startswith("RESULT "):
-            return json.loads(line[7:]), None
-    tail = (r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or ["no output"])[-1]
-    return None, f"exit code {r.returncode}: {tail[:400]}"
+        out, code, tail = r.stdout, r.returncode, r.stderr
+    except subprocess.TimeoutExpired as e:
+        out = e.stdout.decode() if isinstance(e.stdout, bytes) else (e.stdout or "")
+        code, tail = None, ""
+        err = f"no result within {limit_s} s (compile or kernel did not finish)"
+    results = [json.loads(line[7:]) for line in out.splitlines() if line.startswith("RESULT ")]
+    if err is None and len(results) < len(lengths):
+        last = (tail.strip().splitlines() or out.strip().splitlines() or ["no output"])[-1]
+        err = f"exit code {code}: {last[:400]}"
+    return results, err
 
 
 def main():
@@ -101,25 +111,26 @@ def main():
     ap.add_argument("--sets", default="self_s1,self_s05,cross_kv256")
     ap.add_argument("--lengths", default="256,512,1024,2048")
     ap.add_argument("--cell-ms", type=float, default=600.0)
-    ap.add_argument("--limit-s", type=float, default=300.0)
+    ap.add_argument("--limit-s", type=float, default=420.0)
     args = ap.parse_args()
     if args.worker:
-        kind, L, B, mode, cell_ms = args.worker
-        worker(kind, int(L), int(B), mode, float(cell_ms))
+        kind, lengths, B, mode, cell_ms = args.worker
+        worker(kind, [int(x) for x in lengths.split(",")], int(B), mode, float(cell_ms))
         return
     if not os.path.isdir(os.path.join(REF, "ads_mkl", "ops", "oss", "gdpa")):
         print(json.dumps({"impl": "reference_kernel", "unavailable": "baseline/_ref is empty: run baseline/install_reference.sh first"}))
         return
-    cells = [("self_s1", 512, 8, "fwd"), ("self_s1", 512, 8, "bwd")]
+    groups = [("self_s1", [512], 8, "fwd"), ("self_s1", [512], 8, "bwd")]  # a small case first
     if not args.small_only:
-        order = [("self_s1", 2048)] + [(k, int(L)) for k in args.sets.split(",") for L in args.lengths.split(",") if (k, int(L)) != ("self_s1", 2048)]
-        cells += [(k, L, 1152, mode) for k, L in order for mode in ("fwd", "bwd")]
-    for kind, L, B, mode in cells:
-        res, err = run_cell(kind, L, B, mode, args.cell_ms, args.limit_s)
-        if res is None:
-            print(json.dumps({"impl": "reference_kernel", "unavailable": f"ref_{kind}_{mode}_L{L} (B={B}): {err}"}), flush=True)
+        lengths = [int(x) for x in args.lengths.split(",")]
+        groups += [(k, lengths, 1152, mode) for k in args.sets.split(",") for mode in ("fwd", "bwd")]
+    for kind, lengths, B, mode in groups:
+        results, err = run_cells(kind, lengths, B, mode, args.cell_ms, args.limit_s)
+        for res in results:
+            print(json.dumps(res), flush=True)
+        if err is not None:
+            print(json.dumps({"impl": "reference_kernel", "unavailable": f"ref_{kind}_{mode} (B={B}, L={lengths}): {err}"}), flush=True)
             return
-        print(json.dumps(res), flush=True)
 
 
 if __name__ == "__main__":
