@@ -45,9 +45,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # DRAM bytes per Q token of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of
-# 48 sequences of the default workload, H=8, D=128).  Traffic grows in proportion to the tokens, so a full
-# launch is this figure times its Q tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.347e9 / 114351, "gdpa_fwd_kernel": 0.928e9 / 114351}
+# 48 sequences of the default workload, H=8, D=128, with the kernels of commit e5537c8).  Traffic grows in
+# proportion to the tokens, so a full launch is this figure times its Q tokens.
+NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.311e9 / 114351, "gdpa_fwd_kernel": 0.914e9 / 114351}
 
 METRIC = "gdpa_fwd_bwd_useful_tflops"
 UNIT = "TFLOP/s"
@@ -437,6 +437,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--e2e-chunks", type=int, default=32)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
+    ap.add_argument("--head-dim", type=int, default=None, help="override the workload's head_dim (64 or 128; profiling)")
     ap.add_argument("--norms", action="store_true",
                     help="time the forward of the GDPA-plus-norm pipeline (layer norm of Q, Q residual, RMS norm) "
                          "instead of the workload's own pass, and the two row-norm kernels against the HBM roofline")
@@ -508,6 +509,8 @@ def main():
     w = make_workload(args.workload, batch=args.batch)
     if args.activation:
         w.activation = args.activation
+    if args.head_dim:
+        w.head_dim = args.head_dim
     fp8 = args.workload == "c4_fp8_softmax" and not args.mxfp8
     mx = args.workload == "c4_fp8_softmax" and args.mxfp8
     assert not args.mxfp8 or mx, "--mxfp8 goes with --workload c4_fp8_softmax"
