@@ -60,7 +60,7 @@ int device_info(DeviceInfo* out) {
 // `row_stride` / `head_stride` are in elements; 0 means the contiguous default (heads * head_dim and
 // head_dim).  Packed layouts (Q, K, V interleaved along the last dimension) are views with larger strides.
 int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
-              int head_dim, int box_cols, int box_rows, bool swizzle128, long long row_stride = 0,
+              int head_dim, int box_cols, int box_rows, int swizzle_bytes, long long row_stride = 0,
               long long head_stride = 0) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return GDPA_ERR_DRIVER;
@@ -76,7 +76,8 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
   cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), 1u, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                   : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
 }
@@ -85,7 +86,7 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
 int make_tmap_set(TmapSet* set, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
                   int head_dim, int box_cols, long long row_stride = 0, long long head_stride = 0) {
   for (int i = 0; i < kTmapHeights; ++i) {
-    const int rc = make_tmap(&set->m[i], base, dt, elem_bytes, rows, heads, head_dim, box_cols, kTmapRows[i], true, row_stride,
+    const int rc = make_tmap(&set->m[i], base, dt, elem_bytes, rows, heads, head_dim, box_cols, kTmapRows[i], 128, row_stride,
                              head_stride);
     if (rc != GDPA_OK) return rc;
   }
@@ -264,6 +265,11 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   if ((rc = make_tmap_set(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols,
                           no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
     return rc;
+  // output, stored by 32-column x 32-row boxes from the activation warps' staging slabs (64-byte swizzled)
+  for (int i = 0; i < kOutTmapHeights; ++i)
+    if ((rc = make_tmap(&l.tm_o.m[i], p->o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->total_q, p->heads, p->head_dim, 32, 32 >> i,
+                        64)) != GDPA_OK)
+      return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;
   l.args.kv_off = p->kv_offsets;
@@ -493,7 +499,7 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   // fp32 dQ accumulator, reduced into by 32-column x 32-row boxes (128-byte swizzled staging).
   for (int i = 0; i < kDqTmapHeights; ++i)
     if ((rc = make_tmap(&l.tm_dq.m[i], p->dq_accum, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p->total_q, p->heads, p->head_dim, 32,
-                        32 >> i, true)) != GDPA_OK)
+                        32 >> i, 128)) != GDPA_OK)
       return rc;
   l.args.dk = static_cast<__nv_bfloat16*>(p->dk);
   l.args.dv = static_cast<__nv_bfloat16*>(p->dv);

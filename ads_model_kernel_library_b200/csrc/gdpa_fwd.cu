@@ -66,7 +66,12 @@ struct FwdSmem {
   static constexpr int kKvOff = 2 * kTileBytes;
   static constexpr int kRowSumOff = kKvOff + kKvStages * kTileBytes;  // softmax: float[2 Q tiles][2 halves][128]
   static constexpr int kRowMaxOff = kRowSumOff + 4 * kTile * 4;       // softmax, wide: float[2 parity][2][2][128]
-  static constexpr int kBarOff = kRowMaxOff + 8 * kTile * 4;
+  // Output staging of the element-wise kernels, over the softmax arrays (a kernel uses one or the other): one slab of
+  // 32 rows x 32 bf16 per activation warp, 64-byte swizzled, from which that warp's O rows leave by TMA store.
+  static constexpr int kOutSlabBytes = 32 * 64;
+  static constexpr int kOutOff = kRowSumOff;
+  static constexpr int kBarOff = kOutOff + 16 * kOutSlabBytes;
+  static_assert(16 * kOutSlabBytes >= 12 * kTile * 4, "the softmax arrays fit in the staging region");
   static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kBytes = kAbortOff + 4;
@@ -101,9 +106,12 @@ __device__ __forceinline__ float sumsq_bf16x8(const uint4& v) {
 template <int D, int ACT, bool FP8, bool FUSE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ TmapSet tm_k,
-                const __grid_constant__ TmapSet tm_v, const FwdArgs a) {
+                const __grid_constant__ TmapSet tm_v, const __grid_constant__ OutTmapSet tm_o, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
+  // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the softmax kernels
+  // (their row statistics hold that shared memory) and the norm-pipeline epilogue store from registers instead
+  constexpr bool kTmaOut = !kSoftmax && !FUSE;
   constexpr int kActWarps = 16;
   constexpr int kMmaWarp = 16;
   constexpr int kLoadWarp = 17;
@@ -161,6 +169,7 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
     // ------------------------------------------------------------------ TMA loader
     if (lane == 0) {
       uint32_t kv_stage = 0, kv_phase = 0, q_phase = 0;  // bit s of q_phase = parity of Q stage s
+      [[maybe_unused]] int ltr = 0;  // KV tiles before this item (trace rows)
       WorkWalker walker(n_items);
       int idx;
       while (walker.next(idx)) {
@@ -177,7 +186,9 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           if (step == 0 || step == 2) {
             const int s = step >> 1;
             if (s >= nst) continue;
+            GDPA_TRACE(a, ltr * 32 + 24 + s * 2);
             GDPA_WAIT(B_Q_EMPTY + s, ((q_phase >> s) & 1u) ^ 1u, ST_ROLE_LOAD);
+            GDPA_TRACE(a, ltr * 32 + 25 + s * 2);
             q_phase ^= 1u << s;
             const uint32_t bar = bar_base + 8u * (B_Q_FULL + s);
             mbar_arrive_expect_tx(bar, L::kTileBytes);
@@ -204,6 +215,7 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
             }
           }
         }
+        ltr += nkv;
       }
     }
    } else if (warp == kMmaWarp) {
@@ -588,6 +600,7 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
       GDPA_WAIT_WARP(B_O_FULL + s, o_phase, ST_ROLE_EPI);
       o_phase ^= 1u;
       tc_fence_after();
+      if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, (tr - 1) * 32 + s * 8 + 4);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
@@ -598,7 +611,45 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           tc_fence_before();
           mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
         }
-        if (row_valid) {
+        if constexpr (kTmaOut) {
+          // this warp's 32 rows x 32 columns: registers -> its slab (row = 64 bytes, 16-byte pieces XORed with bits 1-2
+          // of the row, the 64-byte swizzle of the tensor map) -> TMA store of the rows that belong to the sequence
+          const uint32_t slab = smem_base + L::kOutOff + warp * L::kOutSlabBytes;
+          uint8_t* const slab_row = smem + L::kOutOff + warp * L::kOutSlabBytes + lane * 64;
+          if (lane == 0) tma_store_wait_read<0>();  // the store that read this slab last has finished reading it
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv_l, __uint_as_float(r[8 * i + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv_l, __uint_as_float(r[8 * i + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv_l, __uint_as_float(r[8 * i + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv_l, __uint_as_float(r[8 * i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(slab_row + ((i ^ ((lane >> 1) & 3)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int slab_rows = w.lq - (qr - lane);  // rows of this warp's 32 inside the sequence
+          if (lane == 0 && slab_rows > 0) {
+            const int x = half * (D / 2) + c * 32, z = static_cast<int>(w.q_start) + qr;
+            if (slab_rows >= 32) {
+              tma_store_3d(&tm_o.m[0], slab, x, w.h, z);
+            } else {
+              // boxes of 16, 8, 4, 2, 1 rows; each starts at an even row of the slab (a multiple of its own height,
+              // and the single row follows an even count), so at a 128-byte boundary
+              int done = 0;
+#pragma unroll 1
+              for (int k = 1; k < kOutTmapHeights; ++k) {
+                const int h = 32 >> k;
+                if (slab_rows - done >= h) {
+                  tma_store_3d(&tm_o.m[k], slab + done * 64, x, w.h, z + done);
+                  done += h;
+                }
+              }
+            }
+            tma_store_commit();
+          }
+        } else if (row_valid) {
           if (!FUSE || (res == nullptr && row_sumsq == nullptr)) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -629,6 +680,7 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
         }
       }
       if (row_sumsq != nullptr && row_valid) atomicAdd(row_sumsq + w.q_start + qr, ssq);
+      if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, (tr - 1) * 32 + s * 8 + 5);
     }
   }
 
@@ -640,6 +692,7 @@ role_done:
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 1000000ull) {}
   }
+  if (kTmaOut && warp < kActWarps && lane == 0) tma_store_wait_all<0>();  // this warp's stores have left shared memory
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -657,7 +710,7 @@ int launch_fwd_fuse(const FwdLaunch& l) {
   auto kernel = gdpa_fwd_kernel<D, ACT, FP8, FUSE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
   if (e != cudaSuccess) return GDPA_ERR_LAUNCH_;
-  kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.args);
+  kernel<<<l.grid, kFwdThreads, L::kDynBytes, l.stream>>>(l.tm_q, l.tm_k, l.tm_v, l.tm_o, l.args);
   return cudaGetLastError() == cudaSuccess ? 0 : GDPA_ERR_LAUNCH_;
 }
 

@@ -29,6 +29,13 @@ struct DqTmapSet {
   CUtensorMap m[kDqTmapHeights];
 };
 
+// The maps of the forward's output: boxes of 32 columns x 32, 16, 8, 4, 2, 1 rows (64-byte swizzle), one activation
+// warp's staging slab; a ragged tile is stored as the boxes that cover exactly the rows of its sequence.
+constexpr int kOutTmapHeights = 6;
+struct OutTmapSet {
+  CUtensorMap m[kOutTmapHeights];
+};
+
 struct FwdArgs {
   __nv_bfloat16* o;
   const void* q_off;
@@ -120,6 +127,7 @@ struct NormBwdArgs {
 
 struct FwdLaunch {
   TmapSet tm_q, tm_k, tm_v;
+  OutTmapSet tm_o;
   FwdArgs args;
   int grid;
   cudaStream_t stream;

@@ -6,6 +6,7 @@ gdpa/src/interface.py:2223 of the reference) timed on the cells of the reference
 
     baseline/install_reference.sh /path/to/ads_model_kernel_library      # once, where the reference is mounted
     python baseline/reference_gpu_arm.py [--small-only] [--sets self_s1,...] [--lengths 256,...]
+    python baseline/reference_gpu_arm.py --accuracy      # forward error of both implementations, one small batch
 
 The reference's kernels are Python DSL sources that compile at their first call, against the nvidia-cutlass-dsl
 package of the machine (the reference pins another version), and their waits have no time limit.  So every cell
@@ -86,6 +87,41 @@ def worker(kind: str, lengths, B: int, mode: str, cell_ms: float) -> None:
         torch.cuda.empty_cache()
 
 
+def accuracy_worker() -> None:
+    """Forward of both implementations on one small batch (B=8, L=512, H=4, D=128, fast_gelu, scale 1) at three input
+    magnitudes, against the same product evaluated in fp32 by torch (tanh form of GELU, gdpa/triton/math.py:150-165
+    of the reference; P not rounded).  One RESULT line per (implementation, magnitude)."""
+    import torch
+
+    sys.path.insert(0, REF)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from ads_mkl.ops.oss.gdpa.src.interface import flash_attn_varlen_func
+    import ads_model_kernel_library_b200.gdpa  # noqa: F401  (registers torch.ops.gdpa)
+    from ads_model_kernel_library_b200.gdpa.math import activation_string_to_int
+
+    B, L, H, D = 8, 512, 4, 128
+    dev = torch.device("cuda", 0)
+    off = (torch.arange(B + 1, dtype=torch.int32) * L).to(dev)
+    act_id = activation_string_to_int("fast_gelu")
+    for std in (0.2, 0.35, 0.5):
+        g = torch.Generator(device=dev).manual_seed(7)
+        q, k, v = ((torch.randn(B * L, H, D, generator=g, device=dev) * std).to(torch.bfloat16) for _ in range(3))
+        qf, kf, vf = (t.float().view(B, L, H, D).permute(0, 2, 1, 3) for t in (q, k, v))
+        s = qf @ kf.transpose(-1, -2)
+        exact = (torch.nn.functional.gelu(s, approximate="tanh") @ vf).permute(0, 2, 1, 3).reshape(B * L, H, D)
+        res = flash_attn_varlen_func(q=q, k=k, v=v, cu_seqlens_q=off, cu_seqlens_k=off, max_seqlen_q=L, max_seqlen_k=L,
+                                     softmax_scale=1.0, activation="fast_gelu")
+        outs = {"reference_kernel": (res[0] if isinstance(res, (tuple, list)) else res).float(),
+                "this_library": torch.ops.gdpa.generalized_dot_product_attention(q, k, v, off, off, L, L, 1.0, act_id).float()}
+        rms = exact.pow(2).mean().sqrt().item()
+        for impl, o in outs.items():
+            err = o - exact
+            print("RESULT " + json.dumps({"impl": impl, "check": "forward against fp32 torch, fast_gelu, scale 1", "input_std": std,
+                                          "score_std": s.std().item(), "share_of_scores_beyond_2": (s.abs() > 2).float().mean().item(),
+                                          "out_rms": rms, "rel_rms_err": err.pow(2).mean().sqrt().item() / rms,
+                                          "max_abs_err": err.abs().max().item()}), flush=True)
+
+
 def run_cells(kind, lengths, B, mode, cell_ms, limit_s):
     """Results of the cells that finished, and an error text if the child failed or ran out of time."""
     cmd = [sys.executable, os.path.abspath(__file__), "--worker", kind, ",".join(str(x) for x in lengths), str(B), mode, str(cell_ms)]
@@ -108,6 +144,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--worker", nargs=5, default=None)
     ap.add_argument("--small-only", action="store_true")
+    ap.add_argument("--accuracy", action="store_true",
+                    help="instead of timing: forward error of the reference's kernel and of this library on one small batch")
     ap.add_argument("--sets", default="self_s1,self_s05,cross_kv256")
     ap.add_argument("--lengths", default="256,512,1024,2048")
     ap.add_argument("--cell-ms", type=float, default=600.0)
@@ -115,10 +153,20 @@ def main():
     args = ap.parse_args()
     if args.worker:
         kind, lengths, B, mode, cell_ms = args.worker
-        worker(kind, [int(x) for x in lengths.split(",")], int(B), mode, float(cell_ms))
+        if kind == "accuracy":
+            accuracy_worker()
+        else:
+            worker(kind, [int(x) for x in lengths.split(",")], int(B), mode, float(cell_ms))
         return
     if not os.path.isdir(os.path.join(REF, "ads_mkl", "ops", "oss", "gdpa")):
         print(json.dumps({"impl": "reference_kernel", "unavailable": "baseline/_ref is empty: run baseline/install_reference.sh first"}))
+        return
+    if args.accuracy:
+        results, err = run_cells("accuracy", [0] * 6, 8, "fwd", 0.0, args.limit_s)
+        for res in results:
+            print(json.dumps(res), flush=True)
+        if err is not None:
+            print(json.dumps({"impl": "reference_kernel", "unavailable": f"accuracy check: {err}"}), flush=True)
         return
     groups = [("self_s1", [512], 8, "fwd"), ("self_s1", [512], 8, "bwd")]  # a small case first
     if not args.small_only:
