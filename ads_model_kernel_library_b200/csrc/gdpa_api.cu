@@ -266,10 +266,8 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
                           no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
     return rc;
   // output, stored by 32-column x 32-row boxes from the activation warps' staging slabs (64-byte swizzled)
-  for (int i = 0; i < kOutTmapHeights; ++i)
-    if ((rc = make_tmap(&l.tm_o.m[i], p->o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->total_q, p->heads, p->head_dim, 32, 32 >> i,
-                        64)) != GDPA_OK)
-      return rc;
+  if ((rc = make_tmap(&l.tm_o.m, p->o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->total_q, p->heads, p->head_dim, 32, 32, 64)) != GDPA_OK)
+    return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;
   l.args.kv_off = p->kv_offsets;

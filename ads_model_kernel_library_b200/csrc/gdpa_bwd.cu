@@ -536,17 +536,19 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
       GDPA_WAIT_WARP(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
       dkv_phase ^= 1u;
       tc_fence_after();
-#pragma unroll
+      // Rolled over the two tensors: this runs once per work item, and the kernel's code size is what the instruction
+      // cache sees in every Q tile.
+#pragma unroll 1
       for (int t = 0; t < 2; ++t) {
         const uint32_t tcol = tmem_base + lane_base + (t == 0 ? kColDV : kColDK) + half * (D / 2);
-        __nv_bfloat16* dst_row = (t == 0 ? dv_row : dk_row) + half * (D / 2);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tcol + c * 32, r);
-          tmem_wait_ld();
-          if constexpr (ACC) {
-            // K / V rows shared between sequences (start / end offsets): every owner adds into fp32 accumulators
+        if constexpr (ACC) {
+          // K / V rows shared between sequences (start / end offsets): every owner adds into fp32 accumulators
+          __nv_bfloat16* dst_row = (t == 0 ? dv_row : dk_row) + half * (D / 2);
+#pragma unroll 1
+          for (int c = 0; c < D / 64; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tcol + c * 32, r);
+            tmem_wait_ld();
             if (row_valid) {
               float* acc_row = (t == 0 ? a.dv_acc : a.dk_acc) + (dst_row - (t == 0 ? a.dv : a.dk)) + c * 32;
 #pragma unroll
@@ -555,7 +557,24 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
                           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                                       __uint_as_float(r[4 * j + 3])));
             }
-          } else if (row_valid) {
+          }
+        } else {
+          // This warp's 32 rows x D/2 columns go through shared memory so that they leave as whole row pieces: 16-byte
+          // stores straight from registers, one row per thread, touch 32 lines per instruction and flood the load/store
+          // unit (measured: the stores and the loads queued behind them cost ~7 000 cycles per work item).  The
+          // staging slab is this warp's own 4 KB of the dS^T buffer, which nothing reads once the item's last dQ
+          // product has completed (it precedes the commit this warp has just waited for); its 16-byte pieces are
+          // XORed with row bits so that neither the row-per-thread writes nor the piece-per-thread reads conflict.
+          // (TMA stores from the slab did the same job on full tiles but, with their two more tensor maps beside the
+          // loader's, slowed ragged KV tiles several-fold.)
+          constexpr int kPieces = D / 16;  // 16-byte pieces per row of D/2 bf16
+          uint8_t* const slab = smem + L::kDsOff + half * L::kHalfBytes + quarter * 4096;
+          auto piece = [](int row_, int chunk) { return row_ * (kPieces * 16) + ((chunk ^ (D == 128 ? (row_ & 7) : ((row_ >> 1) & 3))) << 4); };
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tcol + c * 32, r);
+            tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
@@ -563,9 +582,22 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
               v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
               v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
               v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-              reinterpret_cast<uint4*>(dst_row + c * 32)[j] = v;
+              *reinterpret_cast<uint4*>(slab + piece(lane, c * 4 + j)) = v;
             }
           }
+          __syncwarp();
+          // piece p = i * 32 + lane of the slab: row p / kPieces, 16-byte piece p % kPieces; kPieces neighbouring lanes
+          // write one row's D bytes
+          const int slab_rows = w.lkv - (kv_local - lane);  // rows of this warp's 32 inside the sequence
+          __nv_bfloat16* const out0 = (t == 0 ? dv_row : dk_row) - static_cast<long long>(lane) * a.heads * D + half * (D / 2);
+#pragma unroll 2
+          for (int i = 0; i < kPieces; ++i) {
+            const int prow = (i * 32 + lane) / kPieces, chunk = lane % kPieces;
+            if (prow < slab_rows)
+              *reinterpret_cast<uint4*>(out0 + static_cast<long long>(prow) * a.heads * D + chunk * 8) =
+                  *reinterpret_cast<const uint4*>(slab + piece(prow, chunk));
+          }
+          __syncwarp();  // the slab is rewritten for the next tensor, and by the next item's dS^T
         }
       }
       tc_fence_before();

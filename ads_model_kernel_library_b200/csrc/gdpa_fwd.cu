@@ -106,7 +106,7 @@ __device__ __forceinline__ float sumsq_bf16x8(const uint4& v) {
 template <int D, int ACT, bool FP8, bool FUSE>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ TmapSet tm_k,
-                const __grid_constant__ TmapSet tm_v, const __grid_constant__ OutTmapSet tm_o, const FwdArgs a) {
+                const __grid_constant__ TmapSet tm_v, const __grid_constant__ OutTmap tm_o, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
   // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the softmax kernels
@@ -611,9 +611,12 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           tc_fence_before();
           mbar_arrive(bar_base + 8u * (B_O_EMPTY + s));
         }
-        if constexpr (kTmaOut) {
+        // rows of this warp's 32 inside the sequence (the same for every lane)
+        const int slab_rows = w.lq - (qr - lane);
+        if (kTmaOut && slab_rows >= 32) {
           // this warp's 32 rows x 32 columns: registers -> its slab (row = 64 bytes, 16-byte pieces XORed with bits 1-2
-          // of the row, the 64-byte swizzle of the tensor map) -> TMA store of the rows that belong to the sequence
+          // of the row, the 64-byte swizzle of the tensor map) -> one TMA store.  (A slab that the sequence ends in is
+          // stored from registers below.)
           const uint32_t slab = smem_base + L::kOutOff + warp * L::kOutSlabBytes;
           uint8_t* const slab_row = smem + L::kOutOff + warp * L::kOutSlabBytes + lane * 64;
           if (lane == 0) tma_store_wait_read<0>();  // the store that read this slab last has finished reading it
@@ -629,24 +632,8 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           }
           fence_proxy_async_smem();
           __syncwarp();
-          const int slab_rows = w.lq - (qr - lane);  // rows of this warp's 32 inside the sequence
-          if (lane == 0 && slab_rows > 0) {
-            const int x = half * (D / 2) + c * 32, z = static_cast<int>(w.q_start) + qr;
-            if (slab_rows >= 32) {
-              tma_store_3d(&tm_o.m[0], slab, x, w.h, z);
-            } else {
-              // boxes of 16, 8, 4, 2, 1 rows; each starts at an even row of the slab (a multiple of its own height,
-              // and the single row follows an even count), so at a 128-byte boundary
-              int done = 0;
-#pragma unroll 1
-              for (int k = 1; k < kOutTmapHeights; ++k) {
-                const int h = 32 >> k;
-                if (slab_rows - done >= h) {
-                  tma_store_3d(&tm_o.m[k], slab + done * 64, x, w.h, z + done);
-                  done += h;
-                }
-              }
-            }
+          if (lane == 0) {
+            tma_store_3d(&tm_o.m, slab, half * (D / 2) + c * 32, w.h, static_cast<int>(w.q_start) + qr);
             tma_store_commit();
           }
         } else if (row_valid) {

@@ -29,11 +29,10 @@ struct DqTmapSet {
   CUtensorMap m[kDqTmapHeights];
 };
 
-// The maps of the forward's output: boxes of 32 columns x 32, 16, 8, 4, 2, 1 rows (64-byte swizzle), one activation
-// warp's staging slab; a ragged tile is stored as the boxes that cover exactly the rows of its sequence.
-constexpr int kOutTmapHeights = 6;
-struct OutTmapSet {
-  CUtensorMap m[kOutTmapHeights];
+// The map of the forward's output: boxes of 32 columns x 32 rows (64-byte swizzle), one warp's staging slab.  A slab with fewer than 32 rows of its sequence is stored from registers
+// instead: further maps for smaller boxes, on top of the loaders' own, made the TMA unit refetch descriptors.
+struct OutTmap {
+  CUtensorMap m;
 };
 
 struct FwdArgs {
@@ -127,7 +126,7 @@ struct NormBwdArgs {
 
 struct FwdLaunch {
   TmapSet tm_q, tm_k, tm_v;
-  OutTmapSet tm_o;
+  OutTmap tm_o;
   FwdArgs args;
   int grid;
   cudaStream_t stream;
