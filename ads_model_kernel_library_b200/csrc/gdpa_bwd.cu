@@ -72,7 +72,8 @@ enum BwdBar : int {
   BB_DKV_FULL = 16,
   BB_DKV_EMPTY = 17,// 256 arrivals
   BB_ST_FULL = 18,  // 256 arrivals: softmax, the per-column statistics of a Q tile are in shared memory
-  BB_COUNT = 19
+  BB_LD_TMP = 19,   // the loader's own: a ragged tile has landed and can have its padding rows zeroed
+  BB_COUNT = 20
 };
 
 
@@ -159,6 +160,10 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
   const uint32_t tmem_base = *tmem_ptr;
   const int n_items = a.sched[0];
   const SeqLimits lim = {a.total_q, a.total_kv, 0};
+#ifdef GDPA_ENABLE_TRACE
+  // every CTA's start and end time (ns) in the last 512 slots of the trace buffer
+  if (a.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 256) a.trace[kTraceSlots - 512 + 2 * blockIdx.x] = global_timer_ns();
+#endif
 
   constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
   // S^T / dP^T: A and B both K-major (head dim contiguous), M = N = 128.
@@ -172,8 +177,24 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
     setmaxnreg_dec<kRegsOther>();
     if (warp == kBwdLoadWarp) {
       // ---------------------------------------------------------------- TMA loader
-      if (lane == 0) {
-        uint32_t kv_phase = 0, q_phase = 0 /* bit st = parity of Q stage st */, do_phase = 0, st = 0;
+      // The whole warp walks the items; lane 0 issues the copies.  A full tile goes straight to its consumers'
+      // barrier.  A ragged tile (the last of its sequence) is fetched as the same full boxes onto the loader's own
+      // barrier -- its rows past the sequence end are the next sequence's, or, past the tensor's end, the TMA unit's
+      // zero fill -- then the warp overwrites those rows with zeros in shared memory and only then releases the tile:
+      // the consumers see a zero-padded tile, nothing of the neighbour reaches them, and the tile costs D / 64 copies
+      // plus at most 16 KB of zero stores per box (decomposing it into boxes of its valid rows took up to eleven copies
+      // per box, ~250 cycles each to issue).
+      {
+        uint32_t kv_phase = 0, q_phase = 0 /* bit st = parity of Q stage st */, do_phase = 0, st = 0, tmp_phase = 0;
+        [[maybe_unused]] int ltr = 0;  // trace: Q tiles of the items before this one
+        // zero rows [valid, 128) of `nbox` consecutive boxes at `base` (a box's rows are contiguous 128-byte lines)
+        auto zero_tail = [&](uint8_t* base, int nbox, int valid) {
+          for (int bx = 0; bx < nbox; ++bx)
+            for (int off = valid * 128 + lane * 16; off < L::kHalfBytes; off += 512)
+              *reinterpret_cast<uint4*>(base + bx * L::kHalfBytes + off) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async_smem();
+          __syncwarp();
+        };
         WorkWalker walker(n_items);
         int idx;
         while (walker.next(idx)) {
@@ -184,75 +205,66 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           if (nq == 0) continue;
           const int kv_row = static_cast<int>(w.kv_start) + w.blk * kTile;
           const int q_row = static_cast<int>(w.q_start);
-          GDPA_WAIT(BB_KV_EMPTY, kv_phase ^ 1u, ST_ROLE_LOAD);
+          if (lane == 0) GDPA_TRACE(a, ltr * 32 + 20);
+          GDPA_WAIT_WARP(BB_KV_EMPTY, kv_phase ^ 1u, ST_ROLE_LOAD);
+          if (lane == 0) GDPA_TRACE(a, ltr * 32 + 21);
           kv_phase ^= 1u;
           const int kv_valid = w.lkv - w.blk * kTile;  // rows of this KV tile that belong to the sequence
           {
-            const uint32_t bar = bar_base + 8u * BB_KV_FULL;
-            mbar_arrive_expect_tx(bar, 2 * L::kTileBytes);
-            if (kv_valid >= kTile) {
+            const bool ragged = kv_valid < kTile;
+            if (lane == 0) {
+              const uint32_t bar = bar_base + 8u * (ragged ? BB_LD_TMP : BB_KV_FULL);
+              mbar_arrive_expect_tx(bar, 2 * L::kTileBytes);
 #pragma unroll
               for (int hf = 0; hf < D / 64; ++hf)
                 tma_load_3d(smem_base + L::kKOff + hf * L::kHalfBytes, &tm_k.m[0], bar, hf * 64, w.h, kv_row);
 #pragma unroll
               for (int hf = 0; hf < D / 64; ++hf)
                 tma_load_3d(smem_base + L::kVOff + hf * L::kHalfBytes, &tm_v.m[0], bar, hf * 64, w.h, kv_row);
-            } else {
-              // a ragged tile: the boxes of K, then of V, zero-padded (one rolled loop: rare, and kept small)
-#pragma unroll 1
-              for (int i = 0; i < 2 * (D / 64); ++i) {
-                const bool is_v = i >= D / 64;
-                const int hf = is_v ? i - D / 64 : i;
-                load_box_zero_padded(smem_base + (is_v ? L::kVOff : L::kKOff) + hf * L::kHalfBytes, is_v ? tm_v : tm_k, bar,
-                                     hf * 64, w.h, kv_row, kv_valid, static_cast<int>(a.total_kv));
-              }
+            }
+            if (ragged) {
+              GDPA_WAIT_WARP(BB_LD_TMP, tmp_phase, ST_ROLE_LOAD);
+              tmp_phase ^= 1u;
+              zero_tail(smem + L::kKOff, 2 * (D / 64), kv_valid);  // K and V are neighbours in shared memory
+              if (lane == 0) mbar_arrive(bar_base + 8u * BB_KV_FULL);
             }
           }
+          if (lane == 0) GDPA_TRACE(a, ltr * 32 + 22);
+          ltr += nq;
           for (int m = 0; m < nq; ++m) {
             const int hq = w.h * a.kv_group + m / nq1, mm = m0 + m % nq1;
             const int q_valid = w.lq - mm * kTile;  // rows of this Q / dO tile that belong to the sequence
-            if (q_valid >= kTile) {
-              // a full tile: straight-line code, nothing between a buffer becoming free and its copies being issued
-              GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
-              q_phase ^= 1u << st;
-              {
-                const uint32_t bar = bar_base + 8u * (BB_Q_FULL + st);
-                mbar_arrive_expect_tx(bar, L::kTileBytes);
+            const bool ragged = q_valid < kTile;
+            GDPA_WAIT_WARP(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
+            q_phase ^= 1u << st;
+            if (lane == 0) {
+              const uint32_t bar = bar_base + 8u * (ragged ? BB_LD_TMP : BB_Q_FULL + st);
+              mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-                for (int hf = 0; hf < D / 64; ++hf)
-                  tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q.m[0], bar, hf * 64, hq,
-                              q_row + mm * kTile);
-              }
-              GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
-              do_phase ^= 1u;
-              {
-                const uint32_t bar = bar_base + 8u * BB_DO_FULL;
-                mbar_arrive_expect_tx(bar, L::kTileBytes);
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kQOff + st * L::kTileBytes + hf * L::kHalfBytes, &tm_q.m[0], bar, hf * 64, hq,
+                            q_row + mm * kTile);
+            }
+            if (ragged) {
+              GDPA_WAIT_WARP(BB_LD_TMP, tmp_phase, ST_ROLE_LOAD);
+              tmp_phase ^= 1u;
+              zero_tail(smem + L::kQOff + st * L::kTileBytes, D / 64, q_valid);
+              if (lane == 0) mbar_arrive(bar_base + 8u * (BB_Q_FULL + st));
+            }
+            GDPA_WAIT_WARP(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
+            do_phase ^= 1u;
+            if (lane == 0) {
+              const uint32_t bar = bar_base + 8u * (ragged ? BB_LD_TMP : BB_DO_FULL);
+              mbar_arrive_expect_tx(bar, L::kTileBytes);
 #pragma unroll
-                for (int hf = 0; hf < D / 64; ++hf)
-                  tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do.m[0], bar, hf * 64, hq, q_row + mm * kTile);
-              }
-            } else {
-              // a ragged tile: the Q tile, then the dO tile, zero-padded (one rolled loop: rare, and kept small)
-#pragma unroll 1
-              for (int which = 0; which < 2; ++which) {
-                uint32_t bar;
-                if (which == 0) {
-                  GDPA_WAIT(BB_Q_EMPTY + st, ((q_phase >> st) & 1u) ^ 1u, ST_ROLE_LOAD);
-                  q_phase ^= 1u << st;
-                  bar = bar_base + 8u * (BB_Q_FULL + st);
-                } else {
-                  GDPA_WAIT(BB_DO_EMPTY, do_phase ^ 1u, ST_ROLE_LOAD);
-                  do_phase ^= 1u;
-                  bar = bar_base + 8u * BB_DO_FULL;
-                }
-                mbar_arrive_expect_tx(bar, L::kTileBytes);
-                const uint32_t dst = smem_base + (which == 0 ? L::kQOff + st * L::kTileBytes : L::kDoOff);
-#pragma unroll 1
-                for (int hf = 0; hf < D / 64; ++hf)
-                  load_box_zero_padded(dst + hf * L::kHalfBytes, which == 0 ? tm_q : tm_do, bar, hf * 64, hq, q_row + mm * kTile,
-                                       q_valid, static_cast<int>(a.total_q));
-              }
+              for (int hf = 0; hf < D / 64; ++hf)
+                tma_load_3d(smem_base + L::kDoOff + hf * L::kHalfBytes, &tm_do.m[0], bar, hf * 64, hq, q_row + mm * kTile);
+            }
+            if (ragged) {
+              GDPA_WAIT_WARP(BB_LD_TMP, tmp_phase, ST_ROLE_LOAD);
+              tmp_phase ^= 1u;
+              zero_tail(smem + L::kDoOff, D / 64, q_valid);
+              if (lane == 0) mbar_arrive(bar_base + 8u * BB_DO_FULL);
             }
             st ^= 1u;
           }
@@ -533,9 +545,11 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
         ++tr;
       }
       // dK / dV of this KV tile: TMEM -> bf16 -> global, rows inside the sequence only.
+      if (tracer) GDPA_TRACE(a, (tr - 1) * 32 + 17);
       GDPA_WAIT_WARP(BB_DKV_FULL, dkv_phase, ST_ROLE_ACT);
       dkv_phase ^= 1u;
       tc_fence_after();
+      if (tracer) GDPA_TRACE(a, (tr - 1) * 32 + 18);
       // Rolled over the two tensors: this runs once per work item, and the kernel's code size is what the instruction
       // cache sees in every Q tile.
 #pragma unroll 1
@@ -602,6 +616,7 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
       }
       tc_fence_before();
       mbar_arrive(bar_base + 8u * BB_DKV_EMPTY);
+      if (tracer) GDPA_TRACE(a, (tr - 1) * 32 + 19);
     }
   } else {
     // ------------------------------------------------------------------ dQ reduce warps 0-3
@@ -692,6 +707,9 @@ role_done:
   if (warp < 4 && lane == 0) tma_store_wait_all<0>();  // this warp's reduce-adds have left shared memory
   tc_fence_before();
   __syncthreads();
+#ifdef GDPA_ENABLE_TRACE
+  if (a.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 256) a.trace[kTraceSlots - 511 + 2 * blockIdx.x] = global_timer_ns();
+#endif
   if (warp == kBwdMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);

@@ -53,15 +53,18 @@ __device__ __forceinline__ void seq_bounds(const void* p, int b, int flags, long
   end = load_offset(p, i + 1, flags);
 }
 
-// Cycle stamps for performance analysis: CTA 0 writes clock64() into slot `slot` of the trace buffer
+// Cycle stamps for performance analysis: one CTA (GDPA_TRACE_CTA, default 0) writes clock64() into slot `slot` of the trace buffer
 // when one was registered with gdpa_debug_set_trace().  Compiled in only in builds with -DGDPA_ENABLE_TRACE
 // (the pointer tests sit in the MMA-issuing threads, which are on the critical path of every tile); the
 // default build has none.
 constexpr int kTraceSlots = 16384;
 #ifdef GDPA_ENABLE_TRACE
+#ifndef GDPA_TRACE_CTA
+#define GDPA_TRACE_CTA 0
+#endif
 #define GDPA_TRACE(args, slot)                                                                  \
   do {                                                                                          \
-    if ((args).trace != nullptr && blockIdx.x == 0 && (slot) >= 0 && (slot) < kTraceSlots)     \
+    if ((args).trace != nullptr && blockIdx.x == GDPA_TRACE_CTA && (slot) >= 0 && (slot) < kTraceSlots) \
       (args).trace[(slot)] = clock64();                                                         \
   } while (0)
 #else
