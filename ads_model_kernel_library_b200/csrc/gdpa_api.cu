@@ -82,7 +82,7 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
   return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
 }
 
-// The five maps of one tensor (box heights kTmapRows), for zero-padded tile loads.
+// The map of one operand tensor (TmapSet).
 int make_tmap_set(TmapSet* set, const void* base, CUtensorMapDataType dt, int elem_bytes, long long rows, int heads,
                   int head_dim, int box_cols, long long row_stride = 0, long long head_stride = 0) {
   for (int i = 0; i < kTmapHeights; ++i) {

@@ -30,7 +30,7 @@
 // P^T of column half h is written over the first 32 columns of that half's own S^T columns
 // ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
-// Tiles are loaded zero-padded (load_box_zero_padded): rows of a Q, dO, K or V tile beyond the end of its sequence
+// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a Q, dO, K or V tile beyond the end of its sequence
 // are zeros, not the next sequence's tokens, as with the reference's per-sequence block loads
 // (gdpa/triton/triton_generalized_dot_product_attention.py:1575-1600).  Score entries outside the sequence are
 // therefore S = 0, P = act(0) = 0 and dS = act'(0) x dP with dP = 0: exact zeros with no masking anywhere, and nothing

@@ -154,41 +154,13 @@ __device__ __forceinline__ bool in_window(int q_pos, int kv_pos, int window) {
   return window < 0 || (d <= window && -d <= window);
 }
 
-// Zero-padded tile loads.  A tile of a sequence is 128 rows; the last tile of a sequence holds fewer, and the rows
-// after them in the packed tensor belong to the next sequence.  The reference reads such rows as zero (per-sequence
-// block loads, gdpa/triton/triton_generalized_dot_product_attention.py:270, :317, :1575-1600), and so do these
-// kernels: a ragged tile is fetched as a few smaller boxes that cover exactly its valid rows (one tensor map per box
-// height 128, 64, 16, 4, 1: at most ten copies), and the rest of the tile as boxes that lie beyond the end of the
-// tensor, which the TMA unit fills with zeros, all on the tile's one mbarrier.  Everything downstream then sees a full tile whose padding is exactly zero: score entries
-// outside the sequence are act(0) = 0 and their gradients act'(0) x 0 = 0 with no masking, and nothing of a
-// neighbouring sequence (Inf and NaN included) can reach this one.
-// (TmapSet, the five tensor maps of one tensor, is declared in gdpa_launch.h.)
-
-// One box (128 rows x 128 bytes in shared memory, 128-byte swizzled, at `dst`) of the tile whose first row is `row0`,
-// of which `valid` (1 ... 128) rows belong to the sequence.  `x` / `y` are the column and head coordinates.  A ragged
-// box is two runs of rows, each fetched as boxes of 64, 16, 4 and 1 rows: the valid rows from `row0`, and the padding
-// from beyond the end of the tensor (`rows_total` = its row count), where the TMA unit fills in zeros without reading
-// memory.  Rolled loops: this is the loader thread, which runs ahead of the pipeline, and its code is kept small.
-__device__ __forceinline__ void load_box_zero_padded(uint32_t dst, const TmapSet& tm, uint32_t bar, int x, int y, int row0,
-                                                     int valid, int rows_total) {
-  if (valid >= kTile) {
-    tma_load_3d(dst, &tm.m[0], bar, x, y, row0);
-    return;
-  }
-#pragma unroll 1
-  for (int run = 0; run < 2; ++run) {
-    const int n = run ? kTile - valid : valid;
-    const int row = run ? rows_total : row0;
-    int r = run ? valid : 0;  // row of the box the next copy goes to
-    const int end = r + n;
-#pragma unroll 1
-    for (int k = 1; k < kTmapHeights; ++k) {
-      const int h = 256 >> (2 * k);  // 64, 16, 4, 1
-#pragma unroll 1
-      for (; end - r >= h; r += h) tma_load_3d(dst + r * 128, &tm.m[k], bar, x, y, row + (r - (run ? valid : 0)));
-    }
-  }
-}
+// Zero-padded tiles.  A tile of a sequence is 128 rows; the last tile of a sequence holds fewer, and the rows after
+// them in the packed tensor belong to the next sequence.  The reference reads such rows as zero (per-sequence block
+// loads, gdpa/triton/triton_generalized_dot_product_attention.py:270, :317, :1575-1600), and so do these kernels: the
+// loader warp fetches a ragged tile as full boxes onto a barrier of its own, overwrites the rows past the sequence end
+// with zeros in shared memory, and only then releases the tile to its consumers.  Everything downstream sees a full
+// tile whose padding is exactly zero: score entries outside the sequence are act(0) = 0 and their gradients
+// act'(0) x 0 = 0 with no masking, and nothing of a neighbouring sequence (Inf and NaN included) can reach this one.
 
 // Persistent CTAs walk the longest-first list in a zigzag: round r gives CTA c the item
 // r*G + c on even rounds and r*G + (G-1-c) on odd rounds, so the CTA that drew the longest item of

@@ -21,7 +21,7 @@
 // maxima through shared memory, keep partial row sums and write the log-sum-exp for the backward), and
 // FP8 e4m3 operands with per-128-token-block scales.
 //
-// Tiles are loaded zero-padded (load_box_zero_padded): rows of a tile beyond the end of its sequence are zeros,
+// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a tile beyond the end of its sequence are zeros,
 // not the next sequence's tokens, as with the reference's per-sequence block loads
 // (gdpa/triton/triton_generalized_dot_product_attention.py:270, :317).  So S columns beyond the KV length are
 // exactly 0 and act(0) = 0 for every supported element-wise activation: no masking, and nothing a neighbouring
@@ -53,7 +53,8 @@ enum FwdBar : int {
   B_O_EMPTY = 10 + 2 * kKvStages,      // [2] epilogue (128 arrivals) -> MMA
   B_L_FULL = 12 + 2 * kKvStages,       // [2] softmax: activation group -> epilogue (row sums)
   B_M_FULL = 14 + 2 * kKvStages,       // [2] softmax, wide layout: both column halves have published their row maxima
-  B_COUNT = 16 + 2 * kKvStages
+  B_LD_TMP = 16 + 2 * kKvStages,       // the loader's own: a ragged tile has landed and can have its padding rows zeroed
+  B_COUNT = 17 + 2 * kKvStages
 };
 
 template <int D, int EB>
@@ -167,9 +168,37 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
   if (warp >= kMmaWarp) {
    if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA loader
-    if (lane == 0) {
-      uint32_t kv_stage = 0, kv_phase = 0, q_phase = 0;  // bit s of q_phase = parity of Q stage s
+    // The whole warp walks the items; lane 0 issues the copies.  A full tile goes straight to its consumers' barrier.
+    // A ragged tile (the last of its sequence) is fetched as the same full boxes onto the loader's own barrier -- its
+    // rows past the sequence end are the next sequence's, or, past the tensor's end, the TMA unit's zero fill -- then
+    // the warp overwrites those rows with zeros in shared memory and only then releases the tile: the consumers see a
+    // zero-padded tile and nothing of the neighbour reaches them.
+    {
+      uint32_t kv_stage = 0, kv_phase = 0, q_phase = 0, tmp_phase = 0;  // bit s of q_phase = parity of Q stage s
       [[maybe_unused]] int ltr = 0;  // KV tiles before this item (trace rows)
+      // one tile = L::kBoxes boxes of 128 rows x 128 bytes; `ragged`: onto the loader's barrier, then zero rows >= valid
+      auto load_tile = [&](uint32_t dst_off, const CUtensorMap* tm, int full_bar, int y, int row0, int valid) -> bool {
+        const bool ragged = valid < kTile;
+        if (lane == 0) {
+          const uint32_t bar = bar_base + 8u * (ragged ? B_LD_TMP : full_bar);
+          mbar_arrive_expect_tx(bar, L::kTileBytes);
+#pragma unroll
+          for (int hf = 0; hf < L::kBoxes; ++hf)
+            tma_load_3d(smem_base + dst_off + hf * L::kHalfBytes, tm, bar, hf * L::kBoxCols, y, row0);
+        }
+        if (ragged) {
+          const bool ok = mbar_wait(bar_base + 8u * B_LD_TMP, tmp_phase, abort_flag, a.status, (B_LD_TMP << 8) | ST_ROLE_LOAD);
+          if (!__all_sync(0xffffffffu, ok)) return false;
+          tmp_phase ^= 1u;
+          for (int bx = 0; bx < L::kBoxes; ++bx)
+            for (int off = valid * 128 + lane * 16; off < L::kHalfBytes; off += 512)
+              *reinterpret_cast<uint4*>(smem + dst_off + bx * L::kHalfBytes + off) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_base + 8u * full_bar);
+        }
+        return true;
+      };
       WorkWalker walker(n_items);
       int idx;
       while (walker.next(idx)) {
@@ -186,29 +215,20 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           if (step == 0 || step == 2) {
             const int s = step >> 1;
             if (s >= nst) continue;
-            GDPA_TRACE(a, ltr * 32 + 24 + s * 2);
-            GDPA_WAIT(B_Q_EMPTY + s, ((q_phase >> s) & 1u) ^ 1u, ST_ROLE_LOAD);
-            GDPA_TRACE(a, ltr * 32 + 25 + s * 2);
+            if (lane == 0) GDPA_TRACE(a, ltr * 32 + 24 + s * 2);
+            GDPA_WAIT_WARP(B_Q_EMPTY + s, ((q_phase >> s) & 1u) ^ 1u, ST_ROLE_LOAD);
+            if (lane == 0) GDPA_TRACE(a, ltr * 32 + 25 + s * 2);
             q_phase ^= 1u << s;
-            const uint32_t bar = bar_base + 8u * (B_Q_FULL + s);
-            mbar_arrive_expect_tx(bar, L::kTileBytes);
-            const int valid = w.lq - q0 - s * kTile;  // rows of this Q tile that belong to the sequence
-#pragma unroll 1
-            for (int hf = 0; hf < L::kBoxes; ++hf)
-              load_box_zero_padded(smem_base + L::kQOff + s * L::kTileBytes + hf * L::kHalfBytes, tm_q, bar,
-                                   hf * L::kBoxCols, w.h, q_row + s * kTile, valid, static_cast<int>(a.total_q));
+            if (!load_tile(L::kQOff + s * L::kTileBytes, &tm_q.m[0], B_Q_FULL + s, w.h, q_row + s * kTile,
+                           w.lq - q0 - s * kTile))
+              goto role_done;
           } else {
             const int t = (step == 1) ? 0 : step - 2;  // 0 = K0, 1 = V0, 2 = K1, ...
             const int j = t >> 1;
-            const TmapSet& tm = (t & 1) ? tm_v : tm_k;
-            GDPA_WAIT(B_KV_EMPTY + kv_stage, kv_phase ^ 1u, ST_ROLE_LOAD);
-            const uint32_t bar = bar_base + 8u * (B_KV_FULL + kv_stage);
-            mbar_arrive_expect_tx(bar, L::kTileBytes);
-            const int valid = w.lkv - (j0 + j) * kTile;  // rows of this KV tile that belong to the sequence
-#pragma unroll 1
-            for (int hf = 0; hf < L::kBoxes; ++hf)
-              load_box_zero_padded(smem_base + L::kKvOff + kv_stage * L::kTileBytes + hf * L::kHalfBytes, tm, bar,
-                                   hf * L::kBoxCols, w.h / a.kv_group, kv_row + j * kTile, valid, static_cast<int>(a.total_kv));
+            GDPA_WAIT_WARP(B_KV_EMPTY + kv_stage, kv_phase ^ 1u, ST_ROLE_LOAD);
+            if (!load_tile(L::kKvOff + kv_stage * L::kTileBytes, (t & 1) ? &tm_v.m[0] : &tm_k.m[0], B_KV_FULL + kv_stage,
+                           w.h / a.kv_group, kv_row + j * kTile, w.lkv - (j0 + j) * kTile))
+              goto role_done;
             if (++kv_stage == kKvStages) {
               kv_stage = 0;
               kv_phase ^= 1u;

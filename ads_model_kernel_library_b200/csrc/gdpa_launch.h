@@ -14,10 +14,9 @@ constexpr int GDPA_ERR_UNSUPPORTED_DIM_ = 2;
 constexpr int GDPA_ERR_UNSUPPORTED_ACT_ = 4;
 constexpr int GDPA_ERR_LAUNCH_ = 6;
 
-// The tensor maps of one tensor: boxes of 128, 64, 16, 4 and 1 rows (same box width), so that a tile with fewer
-// than 128 valid rows can be fetched as a few boxes that cover exactly those rows.
-constexpr int kTmapHeights = 5;
-constexpr int kTmapRows[kTmapHeights] = {128, 64, 16, 4, 1};
+// The tensor map of one operand tensor: boxes of 128 rows x 128 bytes (128-byte swizzle).
+constexpr int kTmapHeights = 1;
+constexpr int kTmapRows[kTmapHeights] = {128};
 struct TmapSet {
   CUtensorMap m[kTmapHeights];
 };
