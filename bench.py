@@ -47,7 +47,7 @@ sys.path.insert(0, ROOT)
 # DRAM bytes per Q token of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of
 # 48 sequences of the default workload, H=8, D=128, with the kernels of commit e5537c8).  Traffic grows in
 # proportion to the tokens, so a full launch is this figure times its Q tokens.
-NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.311e9 / 114351, "gdpa_fwd_kernel": 0.914e9 / 114351}
+NCU_DRAM_BYTES_PER_TOKEN = {"gdpa_bwd_kernel": 2.323e9 / 114351, "gdpa_fwd_kernel": 0.929e9 / 114351}
 
 METRIC = "gdpa_fwd_bwd_useful_tflops"
 UNIT = "TFLOP/s"
