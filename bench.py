@@ -434,7 +434,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the number of sequences (reduced-size runs)")
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-chunks", type=int, default=32)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
     ap.add_argument("--head-dim", type=int, default=None, help="override the workload's head_dim (64 or 128; profiling)")
@@ -672,12 +672,15 @@ def main():
 
         e2e_step()
         barrier()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        for _ in range(args.e2e_steps):
+        # every step between its own pair of events; the reported time is the median step (a host hiccup in one step --
+        # these are seconds of host work on a shared machine -- does not decide the number), all steps are listed
+        marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.e2e_steps)]
+        for m0, m1 in marks:
+            m0.record()
             e2e_step()
-        a1.record()
+            m1.record()
         barrier()
+        e2e_steps_ms = [m0.elapsed_time(m1) for m0, m1 in marks]
         # the host's ceiling: the same copies in the same chunks with no kernel between them
         dev_in = {n: torch.empty_like(b[n]) for n in ("q", "k", "v", "do")}
         rows = np.linspace(0, 1, args.e2e_chunks + 1)
@@ -701,7 +704,7 @@ def main():
         copy_only()
         c1.record()
         barrier()
-        te = torch.tensor([a0.elapsed_time(a1) / args.e2e_steps, c0.elapsed_time(c1)], dtype=torch.float64, device=dev)
+        te = torch.tensor([float(np.median(e2e_steps_ms)), c0.elapsed_time(c1)], dtype=torch.float64, device=dev)
         if world > 1:
             all_te = [torch.zeros_like(te) for _ in range(world)]
             dist.all_gather(all_te, te)
@@ -711,6 +714,7 @@ def main():
         copy_ms = max(float(x[1]) for x in all_te)
         e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+               "timed": "median step, max over ranks", "this_rank_steps_ms": [float(x) for x in e2e_steps_ms],
                "per_rank_ms": [float(x[0]) for x in all_te],
                "h2d_gbs_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
                "copy_only_ms_per_step": copy_ms, "copy_only_per_rank_ms": [float(x[1]) for x in all_te],
