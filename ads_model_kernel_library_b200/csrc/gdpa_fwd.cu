@@ -67,12 +67,16 @@ struct FwdSmem {
   static constexpr int kKvOff = 2 * kTileBytes;
   static constexpr int kRowSumOff = kKvOff + kKvStages * kTileBytes;  // softmax: float[2 Q tiles][2 halves][128]
   static constexpr int kRowMaxOff = kRowSumOff + 4 * kTile * 4;       // softmax, wide: float[2 parity][2][2][128]
-  // Output staging of the element-wise kernels, over the softmax arrays (a kernel uses one or the other): one slab of
-  // 32 rows x 32 bf16 per activation warp, 64-byte swizzled, from which that warp's O rows leave by TMA store.
+  // Output staging: one slab of 32 rows x 32 bf16 per activation warp, 64-byte swizzled, from which that warp's O
+  // rows leave by TMA store.  Where shared memory has room the slabs follow the softmax arrays (kSeparate); with
+  // 32 KB bf16 tiles (head_dim 128) it has not, the slabs lie over those arrays, and the softmax kernels of that
+  // shape store O from registers instead.
   static constexpr int kOutSlabBytes = 32 * 64;
-  static constexpr int kOutOff = kRowSumOff;
+  static constexpr int kStatBytes = 12 * kTile * 4;
+  static constexpr bool kSeparate = kRowSumOff + kStatBytes + 16 * kOutSlabBytes + 2048 <= 227 * 1024;
+  static constexpr int kOutOff = kSeparate ? kRowSumOff + kStatBytes : kRowSumOff;
   static constexpr int kBarOff = kOutOff + 16 * kOutSlabBytes;
-  static_assert(16 * kOutSlabBytes >= 12 * kTile * 4, "the softmax arrays fit in the staging region");
+  static_assert(16 * kOutSlabBytes >= kStatBytes, "the softmax arrays fit in the staging region");
   static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kBytes = kAbortOff + 4;
@@ -110,9 +114,10 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
                 const __grid_constant__ TmapSet tm_v, const __grid_constant__ OutTmap tm_o, const FwdArgs a) {
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
-  // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the softmax kernels
-  // (their row statistics hold that shared memory) and the norm-pipeline epilogue store from registers instead
-  constexpr bool kTmaOut = !kSoftmax && !FUSE;
+  // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the bf16 softmax
+  // kernel at head_dim 128 (its row statistics hold that shared memory) and the norm-pipeline epilogue store from
+  // registers instead
+  constexpr bool kTmaOut = !FUSE && (!kSoftmax || FwdSmem<D, FP8 ? 1 : 2>::kSeparate);
   constexpr int kActWarps = 16;
   constexpr int kMmaWarp = 16;
   constexpr int kLoadWarp = 17;
