@@ -524,6 +524,8 @@ int gdpa_bwd(const GdpaBwdParams* p, gdpa_stream_t stream) {
   l.grid = di.sm_count;
   l.stream = st;
   if (cudaMemsetAsync(p->dq_accum, 0, elems_q * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
+  // the kernel hands work items out through a counter in the schedule header (word 3)
+  if (cudaMemsetAsync(static_cast<int*>(const_cast<void*>(p->schedule)) + 3, 0, sizeof(int), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
   if (pairs && cudaMemsetAsync(p->dkv_accum, 0, 2 * elems_kv * sizeof(float), st) != cudaSuccess) return GDPA_ERR_LAUNCH;
   if (act == ACT_SOFTMAX) {
     rc = launch_dpsum(static_cast<const __nv_bfloat16*>(p->d_o), static_cast<const __nv_bfloat16*>(p->o), p->dpsum,

@@ -73,8 +73,11 @@ enum BwdBar : int {
   BB_DKV_EMPTY = 17,// 256 arrivals
   BB_ST_FULL = 18,  // 256 arrivals: softmax, the per-column statistics of a Q tile are in shared memory
   BB_LD_TMP = 19,   // the loader's own: a ragged tile has landed and can have its padding rows zeroed
-  BB_COUNT = 20
+  BB_WORK_FULL = 20,   // [kWorkSlots] the loader has published the index of a work item
+  BB_WORK_EMPTY = 24,  // [kWorkSlots] 13 arrivals: the MMA thread, 8 element-wise and 4 drain warps have read it
+  BB_COUNT = 28
 };
+constexpr int kWorkSlots = 4;
 
 
 template <int D>
@@ -93,7 +96,8 @@ struct BwdSmem {
   static constexpr int kTmemPtrOff = kBarOff + BB_COUNT * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kStatOff = (kAbortOff + 4 + 15) / 16 * 16;  // softmax: float lse[128], dpsum[2][128]
-  static constexpr int kBytes = kStatOff + 3 * kTile * 4;
+  static constexpr int kWorkOff = kStatOff + 3 * kTile * 4;  // int[kWorkSlots]: indices of the work items in flight
+  static constexpr int kBytes = kWorkOff + kWorkSlots * 4;
   static constexpr int kDynBytes = kBytes + 1024;
 };
 
@@ -138,6 +142,7 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
       uint32_t cnt = 1;
       if (i == BB_P_FULL || i == BB_DS_FULL || i == BB_DKV_EMPTY || i == BB_ST_FULL) cnt = 256;
       if (i == BB_DQ_EMPTY) cnt = 128;
+      if (i >= BB_WORK_EMPTY && i < BB_WORK_EMPTY + kWorkSlots) cnt = 13;
       mbar_init(bar_base + 8u * i, cnt);
     }
     *abort_flag = 0;
@@ -164,6 +169,30 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
   // every CTA's start and end time (ns) in the last 512 slots of the trace buffer
   if (a.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 256) a.trace[kTraceSlots - 512 + 2 * blockIdx.x] = global_timer_ns();
 #endif
+
+  // Work items are handed out dynamically: the list is longest first, every CTA starts with item blockIdx.x and takes
+  // its next one from a counter in the schedule header (word 3, zeroed by the entry point before the launch), so a
+  // CTA that runs slower -- SMs differ in what memory latency they see, ragged tiles cost extra -- takes fewer items
+  // instead of finishing late.  The loader warp draws the index and publishes it to the other roles through a small
+  // ring in shared memory; -1 ends the walk.
+  const uint32_t work_ring = smem_base + L::kWorkOff;
+  int* const work_counter = const_cast<int*>(a.sched) + 3;
+  uint32_t work_pos = 0;  // items this role has taken: ring slot = work_pos % kWorkSlots, parity = (work_pos / kWorkSlots) & 1
+  // Consumer side: the index of this role's next work item, -1 at the end of the list, -2 if the wait ran out.
+  // `warp_wide`: called by a whole warp, whose lane 0 releases the slot.  (A function that is not inlined would keep
+  // this out of the roles' code, but register allocation fails for calls in a kernel with fixed register counts.)
+  auto take_work_item = [&](int role, bool warp_wide) -> int {
+    const uint32_t slot = work_pos % kWorkSlots, parity = (work_pos / kWorkSlots) & 1u;
+    ++work_pos;
+    bool ok = mbar_wait(bar_base + 8u * (BB_WORK_FULL + slot), parity, abort_flag, a.status, ((BB_WORK_FULL + slot) << 8) | role);
+    if (warp_wide) ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return -2;
+    int idx;
+    asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(idx) : "r"(work_ring + 4u * slot) : "memory");
+    if (warp_wide) __syncwarp();
+    if (!warp_wide || lane == 0) mbar_arrive(bar_base + 8u * (BB_WORK_EMPTY + slot));
+    return idx;
+  };
 
   constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
   // S^T / dP^T: A and B both K-major (head dim contiguous), M = N = 128.
@@ -195,9 +224,28 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
           fence_proxy_async_smem();
           __syncwarp();
         };
-        WorkWalker walker(n_items);
-        int idx;
-        while (walker.next(idx)) {
+        // producer side of the work ring: the slot must have been read by every consumer of its previous use
+        auto draw_item = [&](int& idx) -> bool {
+          const uint32_t slot = work_pos % kWorkSlots, parity = (work_pos / kWorkSlots) & 1u;
+          const bool ok = mbar_wait(bar_base + 8u * (BB_WORK_EMPTY + slot), parity ^ 1u, abort_flag, a.status,
+                                    ((BB_WORK_EMPTY + slot) << 8) | ST_ROLE_LOAD);
+          if (!__all_sync(0xffffffffu, ok)) return false;
+          int i = 0;
+          if (lane == 0) {
+            i = work_pos == 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(work_counter, 1);
+            if (i >= n_items) i = -1;
+            asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(work_ring + 4u * slot), "r"(i) : "memory");
+            mbar_arrive(bar_base + 8u * (BB_WORK_FULL + slot));
+          }
+          idx = __shfl_sync(0xffffffffu, i, 0);
+          ++work_pos;
+          return true;
+        };
+        int idx, idx_next;
+        if (!draw_item(idx)) goto role_done;
+        for (; idx >= 0; idx = idx_next) {
+          // the next index is drawn now, a whole work item ahead of its use
+          if (!draw_item(idx_next)) goto role_done;
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
           int m0, nq1;  // first Q tile and number of Q tiles of one query head this item visits
           bwd_q_range(w, a.window, m0, nq1);
@@ -293,9 +341,11 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
                         kk > 0 ? 1u : 0u);
           }
         };
-        WorkWalker walker(n_items);
         int idx;
-        while (walker.next(idx)) {
+        while (true) {
+          idx = take_work_item(ST_ROLE_MMA, false);
+          if (idx == -2) goto role_done;
+          if (idx < 0) break;
           const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
           int m0, nq1;
           bwd_q_range(w, a.window, m0, nq1);
@@ -390,9 +440,11 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
     float* stat_dps = stat_lse + kTile;  // two buffers, by parity of the Q tile
     const int ew_tid = threadIdx.x - 128;  // 0..255 among the element-wise threads
     const float c2 = a.scale * 1.4426950408889634f;
-    WorkWalker walker(n_items);
     int idx;
-    while (walker.next(idx)) {
+    while (true) {
+      idx = take_work_item(ST_ROLE_ACT, true);
+      if (idx == -2) goto role_done;
+      if (idx < 0) break;
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
       int m0, nq1;
       bwd_q_range(w, a.window, m0, nq1);
@@ -628,9 +680,11 @@ gdpa_bwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
     const uint32_t stage_base = smem_base + L::kDqOff + warp * (2 * kDqWarpSlabBytes);
     uint32_t dq_phase = 0, slab = 0;
     int tr = 0;
-    WorkWalker walker(n_items);
     int idx;
-    while (walker.next(idx)) {
+    while (true) {
+      idx = take_work_item(ST_ROLE_RED, true);
+      if (idx == -2) goto role_done;
+      if (idx < 0) break;
       const Work w = load_work(a.sched, idx, a.q_off, a.kv_off, a.off64, a.max_q, a.max_kv, lim);
       int m0, nq1;
       bwd_q_range(w, a.window, m0, nq1);

@@ -377,7 +377,11 @@ typedef struct GdpaBwdParams {
   int32_t max_seq_len_kv;
   int32_t activation;
   float qk_scale;
-  const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_BWD) */
+  const void* schedule;       /* from gdpa_build_schedule(GDPA_SCHED_BWD).  gdpa_bwd writes one word of its header:
+                               * the kernel hands work items to its CTAs through a counter there, which gdpa_bwd
+                               * zeroes on the stream before the launch.  The list itself is only read and may be
+                               * reused by later calls, but two gdpa_bwd calls that can run at the same time need
+                               * a schedule buffer each. */
   void* dq_accum;             /* scratch: gdpa_bwd_workspace_bytes() bytes; zeroed by gdpa_bwd */
   int32_t* status;
   /* Optional cudaEvent_t pair recorded around the main backward kernel only (not around the
