@@ -92,7 +92,16 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self, wait_s: float = 3.0) -> int:
+        """Waits (bounded) until nvidia-smi has delivered its first sample -- its start-up can take longer than a short
+        timed region -- and returns the number of samples so far: `stop(first=...)` then keeps only later ones."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < wait_s:
+            time.sleep(0.02)
+        return len(self.lines)
+
+    def stop(self, first: int = 0):
+        self.lines = self.lines[first:] if first < len(self.lines) else self.lines[-1:]
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -434,7 +443,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="override the number of sequences (reduced-size runs)")
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-chunks", type=int, default=32)
     ap.add_argument("--activation", default=None, help="override the workload's activation (experiments)")
     ap.add_argument("--head-dim", type=int, default=None, help="override the workload's head_dim (64 or 128; profiling)")
@@ -570,6 +579,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler starts before the warm-up, so that it is delivering samples when the timed region begins
+    sampler = ClockSampler(_gpu_index(local_rank))
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
@@ -579,10 +592,8 @@ def main():
     fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     bwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(_gpu_index(local_rank))
     launches0 = _cabi.lib.gdpa_launch_count()
-    if rank == 0:
-        sampler.start()
+    first_sample = sampler.mark() if rank == 0 else 0
     barrier()
     e0.record()
     for i in range(args.steps):
@@ -590,7 +601,7 @@ def main():
             step()
     e1.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(first_sample) if rank == 0 else None
     launches = _cabi.lib.gdpa_launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
     tt = torch.tensor([ms_total], dtype=torch.float64, device=dev)
