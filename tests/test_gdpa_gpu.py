@@ -563,3 +563,33 @@ def test_timed_out_wait_is_raised_by_the_next_operator_call(G):
         G.generalized_dot_product_attention(dev["q"], dev["k"], dev["v"], dev["qo"], dev["ko"], 100, 100, activation="relu")
     o = run_fwd(G, dev, [100], [100], "relu", 0.1)  # the word was cleared by the raise
     assert_close(o, oracle_forward(cpu, "relu", 0.1), "O after a reported time-out")
+
+
+def test_backward_schedule_can_be_reused_by_later_calls(G, monkeypatch):
+    """The backward kernel draws its work items from a counter in the schedule header, which gdpa_bwd zeroes before
+    every launch: a schedule built once serves any number of calls (one at a time).  Batches of fewer and of many more
+    work items than the GPU has SMs."""
+    from ads_model_kernel_library_b200.gdpa import ops
+
+    built = {}
+    real = ops._build_schedule
+
+    def cached(mode, qo, ko, *rest, **kw):
+        key = (mode, qo.data_ptr(), ko.data_ptr())
+        if key not in built:
+            built[key] = real(mode, qo, ko, *rest, **kw)
+        return built[key]
+
+    monkeypatch.setattr(ops, "_build_schedule", cached)
+    for lens in ([300, 1, 129], list(np.random.default_rng(3).integers(1, 700, 96))):
+        built.clear()
+        cpu, dev = jagged_inputs(lens, lens, 4, 128, seed=11, std=0.5)
+        lens = [int(x) for x in lens]
+        ref = oracle_forward_backward(cpu, "gelu_approx", 1.0 / 128)
+        grads = [run_fwd_bwd(G, dev, lens, lens, "gelu_approx", 1.0 / 128)[1:] for _ in range(3)]
+        assert len(built) == 2  # one forward and one backward schedule, built once
+        for g, e, name in zip(grads[-1], ref[1:], ("dq", "dk", "dv")):
+            assert_close(g, e, name)
+        # dK and dV are sums in a fixed order: identical from call to call; dQ is added up by reduce operations
+        assert torch.equal(grads[0][1], grads[2][1]) and torch.equal(grads[0][2], grads[2][2])
+        torch.testing.assert_close(grads[0][0].float(), grads[2][0].float(), atol=2e-2, rtol=2e-2)
