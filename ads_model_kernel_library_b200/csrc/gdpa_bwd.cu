@@ -1,8 +1,8 @@
 // GDPA backward for sm_100a: dQ, dK, dV of  O = cast(act(Q K^T) * scale) V  over a jagged batch,
 // with S and P recomputed (nothing but Q, K, V, dO is read).
 //
-// One persistent CTA per SM walks a longest-first list of work items (sequence, head, 128-row KV
-// tile).  The item's K and V tiles stay resident in shared memory; the Q tiles of the sequence stream
+// One persistent CTA per SM takes work items (sequence, head, 128-row KV tile) from a longest-first list: its first
+// by its index, the following ones from a counter in the list's header.  The item's K and V tiles stay resident in shared memory; the Q tiles of the sequence stream
 // through a two-stage ring, the dO tiles through one stage (with grouped-query attention the item walks
 // the Q tiles of every query head of its group; with a band only the Q tiles the band can reach).
 // Per Q tile m the tensor cores run five contractions, with the KV rows as the M dimension of the
@@ -19,19 +19,21 @@
 // (P = act(S) scale, act'(S) scale, dS = act' dP) overlaps the contractions of tile m-1 and m+1.
 // dQ tiles are drained by a dedicated warpgroup (whole tile into registers, TMEM released, then each
 // warp stages its 32 rows in shared memory) and added into an fp32 accumulator by TMA reduce-add; a
-// second kernel rounds the accumulator to bf16.  Q rows of a ragged tile beyond the sequence are not touched: the reduce
-// of such a tile covers exactly the rows of the sequence (smaller boxes).
+// second kernel rounds the accumulator to bf16.  Q rows of a ragged tile beyond the sequence are not touched: the
+// reduce of such a tile covers exactly the rows of the sequence (smaller boxes).
 //
 // Softmax: P^T = 2^(c S^T - lse[q]) from the forward's log-sum-exp and dS = scale P (dP - dPsum[q]); the
 // per-column statistics of a Q tile reach the element-wise warps through shared memory.
 //
 // Roles (16 warps, setmaxnreg 144 / 144 / 80): warps 0-3 dQ reduce, warps 4-11 element-wise (warp w:
-// TMEM lanes 32*(w%4), score columns 64*((w-4)/4)), warp 12 MMA issuer, warp 13 TMA loader, warps 14-15 idle.
+// TMEM lanes 32*(w%4), score columns 64*((w-4)/4); at the end of a work item they write dK and dV out through their own
+// part of the dS^T buffer), warp 12 MMA issuer (one lane), warp 13 TMA loader (lane 0 issues the copies and draws the
+// work items, the warp zeroes the tails of ragged tiles), warps 14-15 idle.
 // P^T of column half h is written over the first 32 columns of that half's own S^T columns
 // ([64h, 64h+32)), so the two halves never touch each other's unread scores.
 //
-// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a Q, dO, K or V tile beyond the end of its sequence
-// are zeros, not the next sequence's tokens, as with the reference's per-sequence block loads
+// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a
+// Q, dO, K or V tile beyond the end of its sequence are zeros, not the next sequence's tokens, as with the reference's per-sequence block loads
 // (gdpa/triton/triton_generalized_dot_product_attention.py:1575-1600).  Score entries outside the sequence are
 // therefore S = 0, P = act(0) = 0 and dS = act'(0) x dP with dP = 0: exact zeros with no masking anywhere, and nothing
 // a neighbouring sequence holds (Inf and NaN included) reaches this one.  (Softmax: P = 2^(0 - lse) is not zero there,

@@ -6,11 +6,12 @@
 //
 //   warps 0-7   activation of Q tile 0: S0 (TMEM) -> registers -> act * scale -> bf16 P0 (TMEM); two
 //               warps per TMEM lane quarter, each owning 64 of the 128 S columns.  At the end of a work
-//               item the same warps drain their half of O0 (TMEM -> bf16 -> global).
+//               item the same warps drain their half of O0 (TMEM -> bf16 -> a staging slab in shared memory ->
+//               TMA store).
 //   warps 8-15  the same for Q tile 1
 //   warp  16    MMA issuer (one lane): S_s = Q_s K^T (tcgen05.mma, operands in shared memory),
 //               O_s += P_s V (A operand P read from TMEM)
-//   warp  17    TMA loader (one lane);  warps 18-19 idle
+//   warp  17    TMA loader (lane 0 issues the copies, the warp zeroes the tails of ragged tiles);  warps 18-19 idle
 //
 // TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+D)  O1 [384,384+D).  P_s (bf16, two
 // values per column) of column half h overwrites the first 32 columns of that half's own S columns.
@@ -21,8 +22,8 @@
 // maxima through shared memory, keep partial row sums and write the log-sum-exp for the backward), and
 // FP8 e4m3 operands with per-128-token-block scales.
 //
-// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a tile beyond the end of its sequence are zeros,
-// not the next sequence's tokens, as with the reference's per-sequence block loads
+// Tiles reach their consumers zero-padded (the loader zeroes the tail of a ragged tile in shared memory): rows of a
+// tile beyond the end of its sequence are zeros, not the next sequence's tokens, as with the reference's per-sequence block loads
 // (gdpa/triton/triton_generalized_dot_product_attention.py:270, :317).  So S columns beyond the KV length are
 // exactly 0 and act(0) = 0 for every supported element-wise activation: no masking, and nothing a neighbouring
 // sequence holds (Inf and NaN included) reaches this one.  Only the softmax (where a padded column must not count)
