@@ -173,3 +173,38 @@ def test_flop_formula_counts_valid_pairs_only():
     assert ops._valid_pairs(qo, ko, 4, 100) == 3 * 5 + 4 * 4  # clamped to max_seq_len_q
     meta = torch.empty(3, device="meta", dtype=torch.int64)
     assert ops._valid_pairs(meta, meta, 8, 16) == 2 * 8 * 16
+
+
+def test_clock_sampler_keeps_the_samples_of_the_timed_region_only():
+    """bench.py starts nvidia-smi before the warm-up (its start-up can outlast a short timed region) and keeps the
+    samples that arrive after the mark it takes when the timed region begins; the reported clock is the median of the
+    samples under load."""
+    import sys
+
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    import bench
+
+    class Proc:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+    s = bench.ClockSampler(0)
+    s.proc = Proc()
+    idle = "1965, 1965, 200.0, Not Active, Not Active, Not Active, Not Active"
+    s.lines = [idle] * 3
+    first = s.mark(0.0)
+    assert first == 3
+    s.lines += ["1500, 1965, 700.0, Not Active, Not Active, Not Active, Active", idle,
+                "1520, 1965, 720.0, Not Active, Not Active, Not Active, Active"]
+    out = s.stop(first)
+    assert out["samples"] == 3 and out["samples_under_load"] == 2
+    assert out["sm_mhz"] == 1510.0 and out["sm_max_mhz"] == 1965.0 and out["reasons"] == ["sw_power_cap"]
+    # no sample after the mark: the last one before it is kept rather than none
+    s2 = bench.ClockSampler(0)
+    s2.proc = Proc()
+    s2.lines = [idle] * 2
+    assert s2.stop(s2.mark(0.0))["samples"] == 1
