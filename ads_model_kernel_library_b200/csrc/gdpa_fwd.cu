@@ -116,8 +116,8 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
   // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the bf16 softmax
-  // kernel at head_dim 128 (its row statistics hold that shared memory) and the norm-pipeline epilogue store from
-  // registers instead
+  // kernel at head_dim 128 (its row statistics hold that shared memory) stores from registers instead; the
+  // norm-pipeline epilogue has its own path through the same slabs
   constexpr bool kTmaOut = !FUSE && (!kSoftmax || FwdSmem<D, FP8 ? 1 : 2>::kSeparate);
   constexpr int kActWarps = 16;
   constexpr int kMmaWarp = 16;
@@ -622,6 +622,24 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
         if ((threadIdx.x & 255) == 0) GDPA_TRACE(a, tr * 32 + s * 8 + 3);
         ++tr;
       }
+      // Norm pipeline, a warp whose 32 rows all belong to the sequence: its residual rows are fetched now, under the
+      // wait for the last P V, as whole 64-byte row pieces (four neighbouring lanes per piece), and turned into one row
+      // per thread through the staging slab below.  Piece p = i * 32 + lane: row p / 4, 16-byte chunk p % 4.
+      [[maybe_unused]] uint4 rres[D / 64][4];
+      [[maybe_unused]] const bool fuse_staged = FUSE && (w.lq - (qr - lane) >= 32);
+      if constexpr (FUSE) {
+        if (fuse_staged && a.residual != nullptr) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int p = i * 32 + lane;
+              rres[c][i] = *reinterpret_cast<const uint4*>(
+                  a.residual + ((w.q_start + (qr - lane) + (p >> 2)) * a.heads + w.h) * static_cast<long long>(D) + half * (D / 2) +
+                  c * 32 + (p & 3) * 8);
+            }
+        }
+      }
       // epilogue: this warp's half of the O tile, TMEM -> bf16 -> global
       GDPA_WAIT_WARP(B_O_FULL + s, o_phase, ST_ROLE_EPI);
       o_phase ^= 1u;
@@ -655,6 +673,45 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
             v.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv_l, __uint_as_float(r[8 * i + 5]) * inv_l);
             v.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv_l, __uint_as_float(r[8 * i + 7]) * inv_l);
             *reinterpret_cast<uint4*>(slab_row + ((i ^ ((lane >> 1) & 3)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tm_o.m, slab, half * (D / 2) + c * 32, w.h, static_cast<int>(w.q_start) + qr);
+            tma_store_commit();
+          }
+        } else if (FUSE && fuse_staged) {
+          // the norm pipeline's epilogue through the same slab: residual pieces in, one row per thread out, x = O + residual
+          // and its bf16 back in, one TMA store
+          const uint32_t slab = smem_base + L::kOutOff + warp * L::kOutSlabBytes;
+          uint8_t* const slab_base = smem + L::kOutOff + warp * L::kOutSlabBytes;
+          uint8_t* const slab_row = slab_base + lane * 64;
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          uint4 own[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+          if (a.residual != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int p = i * 32 + lane, prow = p >> 2;
+              *reinterpret_cast<uint4*>(slab_base + prow * 64 + (((p & 3) ^ ((prow >> 1) & 3)) << 4)) = rres[c][i];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) own[i] = *reinterpret_cast<const uint4*>(slab_row + ((i ^ ((lane >> 1) & 3)) << 4));
+            __syncwarp();
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t rw[4] = {own[i].x, own[i].y, own[i].z, own[i].w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float x0 = fmaf(__uint_as_float(r[8 * i + 2 * j]), inv_l, __uint_as_float(rw[j] << 16));
+              const float x1 = fmaf(__uint_as_float(r[8 * i + 2 * j + 1]), inv_l, __uint_as_float(rw[j] & 0xffff0000u));
+              ssq = fmaf(x0, x0, fmaf(x1, x1, ssq));
+              ow[j] = pack_bf16x2(x0, x1);
+            }
+            *reinterpret_cast<uint4*>(slab_row + ((i ^ ((lane >> 1) & 3)) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -705,7 +762,7 @@ role_done:
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 1000000ull) {}
   }
-  if (kTmaOut && warp < kActWarps && lane == 0) tma_store_wait_all<0>();  // this warp's stores have left shared memory
+  if ((kTmaOut || FUSE) && warp < kActWarps && lane == 0) tma_store_wait_all<0>();  // this warp's stores have left shared memory
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
