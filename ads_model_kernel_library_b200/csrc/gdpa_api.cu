@@ -77,7 +77,8 @@ int make_tmap(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                   : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                   : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? GDPA_OK : GDPA_ERR_DRIVER;
 }
@@ -265,8 +266,11 @@ static int fwd_common(const GdpaFwdParams* p, gdpa_stream_t stream, bool fp8) {
   if ((rc = make_tmap_set(&l.tm_v, vp, dt, eb, kv_rows, kvh_map, p->head_dim, box_cols,
                           no_kv ? p->q_strides[0] : p->v_strides[0], no_kv ? p->q_strides[1] : p->v_strides[1])) != GDPA_OK)
     return rc;
-  // output, stored by 32-column x 32-row boxes from the activation warps' staging slabs (64-byte swizzled)
-  if ((rc = make_tmap(&l.tm_o.m, p->o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->total_q, p->heads, p->head_dim, 32, 32, 64)) != GDPA_OK)
+  // output, stored by 32-column x 32-row boxes from the activation warps' staging slabs (64-byte swizzled); the bf16
+  // softmax kernel at head_dim 128 has room for 16-column slabs only (32-byte swizzled)
+  const bool narrow_out = !fp8 && act == ACT_SOFTMAX && p->head_dim == 128;
+  if ((rc = make_tmap(&l.tm_o.m, p->o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p->total_q, p->heads, p->head_dim, narrow_out ? 16 : 32,
+                      32, narrow_out ? 32 : 64)) != GDPA_OK)
     return rc;
   l.args.o = static_cast<__nv_bfloat16*>(p->o);
   l.args.q_off = p->q_offsets;

@@ -76,6 +76,10 @@ struct FwdSmem {
   static constexpr int kStatBytes = 12 * kTile * 4;
   static constexpr bool kSeparate = kRowSumOff + kStatBytes + 16 * kOutSlabBytes + 2048 <= 227 * 1024;
   static constexpr int kOutOff = kSeparate ? kRowSumOff + kStatBytes : kRowSumOff;
+  // ... and there the softmax kernel has narrow slabs of its own behind its arrays: 32 rows x 16 bf16 (32-byte swizzle)
+  static constexpr int kNarrowSlabBytes = 32 * 32;
+  static constexpr int kNarrowOff = kRowSumOff + kStatBytes;
+  static_assert(kStatBytes + 16 * kNarrowSlabBytes <= 16 * kOutSlabBytes, "the narrow slabs fit in the staging region");
   static constexpr int kBarOff = kOutOff + 16 * kOutSlabBytes;
   static_assert(16 * kOutSlabBytes >= kStatBytes, "the softmax arrays fit in the staging region");
   static constexpr int kTmemPtrOff = kBarOff + B_COUNT * 8;
@@ -116,9 +120,10 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
   constexpr int EB = FP8 ? 1 : 2;
   constexpr bool kSoftmax = (ACT == ACT_SOFTMAX);
   // O leaves through shared memory and TMA stores (whole 64-byte row pieces per transaction); the bf16 softmax
-  // kernel at head_dim 128 (its row statistics hold that shared memory) stores from registers instead; the
-  // norm-pipeline epilogue has its own path through the same slabs
-  constexpr bool kTmaOut = !FUSE && (!kSoftmax || FwdSmem<D, FP8 ? 1 : 2>::kSeparate);
+  // kernel at head_dim 128 (its row statistics hold that shared memory) has narrower slabs of its own (32-byte row
+  // pieces); the norm-pipeline epilogue has its own path through the wide slabs
+  constexpr bool kNarrowOut = !FUSE && kSoftmax && !FwdSmem<D, FP8 ? 1 : 2>::kSeparate;
+  constexpr bool kTmaOut = !FUSE && !kNarrowOut;
   constexpr int kActWarps = 16;
   constexpr int kMmaWarp = 16;
   constexpr int kLoadWarp = 17;
@@ -680,6 +685,32 @@ gdpa_fwd_kernel(const __grid_constant__ TmapSet tm_q, const __grid_constant__ Tm
             tma_store_3d(&tm_o.m, slab, half * (D / 2) + c * 32, w.h, static_cast<int>(w.q_start) + qr);
             tma_store_commit();
           }
+        } else if (kNarrowOut && slab_rows >= 32) {
+          // the same with this variant's narrow slab: 16 columns at a time, 32-byte rows whose two 16-byte pieces swap
+          // places in every other group of four rows (the tensor map's 32-byte swizzle)
+          const uint32_t slab = smem_base + L::kNarrowOff + warp * L::kNarrowSlabBytes;
+          uint8_t* const slab_row = smem + L::kNarrowOff + warp * L::kNarrowSlabBytes + lane * 32;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int e = 16 * h2 + 8 * i;
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[e + 0]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(slab_row + ((i ^ ((lane >> 2) & 1)) << 4)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_o.m, slab, half * (D / 2) + c * 32 + h2 * 16, w.h, static_cast<int>(w.q_start) + qr);
+              tma_store_commit();
+            }
+          }
         } else if (FUSE && fuse_staged) {
           // the norm pipeline's epilogue through the same slab: residual pieces in, one row per thread out, x = O + residual
           // and its bf16 back in, one TMA store
@@ -762,7 +793,7 @@ role_done:
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 1000000ull) {}
   }
-  if ((kTmaOut || FUSE) && warp < kActWarps && lane == 0) tma_store_wait_all<0>();  // this warp's stores have left shared memory
+  if ((kTmaOut || kNarrowOut || FUSE) && warp < kActWarps && lane == 0) tma_store_wait_all<0>();  // this warp's stores have left shared memory
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
